@@ -1,0 +1,98 @@
+// Shared host/device definitions for the SplitD attention kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sd {
+
+constexpr int kHeadDim = 512;
+constexpr int kRowsPerCta = 64;          // packed query rows one CTA of a pair owns (UMMA M = 128 per pair)
+constexpr int kRowsPerPair = 2 * kRowsPerCta;
+constexpr int kChunkElems = 64;          // one 128-byte swizzle span of bf16/fp16
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Query rows are "packed": for a KV head with G query heads, row r of a tile is
+// (position r / G, query head r % G), so one tile of 128 rows shares one K/V stream
+// (the reference folds heads into rows the same way, src/pack_gqa.py:16-41).
+// pack_g == 1 means no folding: a tile is 128 positions of a single query head.
+struct TileGeom {
+  int batch;
+  int seqlen_q, seqlen_k;  // batched lengths; packed layout: maxima
+  int heads_q, heads_kv;
+  int group;               // heads_q / heads_kv
+  int pack_g;              // heads folded into rows (group, or 1)
+  int head_units;          // heads_kv if folded else heads_q
+  int pos_per_cta;         // 64 / pack_g
+  int causal;
+  const int* cu_q;         // nullptr => batched
+  const int* cu_k;
+  int row_tiles;           // batched: tiles per sequence; packed: upper bound over all sequences
+};
+
+struct FwdParams {
+  TileGeom g;
+  void* o;
+  float* lse;
+  int64_t o_stride_b, o_stride_s, o_stride_h;  // elements
+  int total_q;                                 // packed: T (lse row pitch)
+  float scale_log2;                            // softmax_scale * log2(e)
+  int* status;
+  float* debug;
+};
+
+// Which tile does this CTA pair work on. Returns false when the pair has nothing to do.
+struct TileCoord {
+  int b, hu, hkv;
+  int p0;        // first position of the pair's tile (sequence-relative)
+  int sq, sk;    // this sequence's lengths
+  int q_off, k_off;  // token offsets of the sequence in the packed tensors (0 when batched)
+};
+
+__device__ __forceinline__ bool decode_tile(const TileGeom& g, int pair_id, TileCoord& t) {
+  const int pos_per_pair = 2 * g.pos_per_cta;
+  int hu, b, rt;
+  if (g.cu_q == nullptr) {
+    const int bh = pair_id / g.row_tiles;
+    rt = pair_id - bh * g.row_tiles;
+    b = bh / g.head_units;
+    hu = bh - b * g.head_units;
+    if (b >= g.batch) return false;
+    t.sq = g.seqlen_q;
+    t.sk = g.seqlen_k;
+    t.q_off = 0;
+    t.k_off = 0;
+    if (g.causal) rt = g.row_tiles - 1 - rt;  // heaviest tiles first
+  } else {
+    hu = pair_id / g.row_tiles;
+    int idx = pair_id - hu * g.row_tiles;
+    if (hu >= g.head_units) return false;
+    int acc = 0;
+    b = -1;
+    int nt = 0;
+    for (int i = 0; i < g.batch; ++i) {
+      const int q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
+      nt = (q1 - q0 + pos_per_pair - 1) / pos_per_pair;
+      if (idx < acc + nt) {
+        b = i;
+        t.q_off = q0;
+        t.sq = q1 - q0;
+        break;
+      }
+      acc += nt;
+    }
+    if (b < 0) return false;
+    rt = idx - acc;
+    if (g.causal) rt = nt - 1 - rt;
+    t.k_off = g.cu_k[b];
+    t.sk = g.cu_k[b + 1] - t.k_off;
+  }
+  t.b = b;
+  t.hu = hu;
+  t.hkv = (g.pack_g == g.group) ? hu : hu / g.group;  // folded: hu is the KV head already
+  t.p0 = rt * pos_per_pair;
+  return true;
+}
+
+}  // namespace sd

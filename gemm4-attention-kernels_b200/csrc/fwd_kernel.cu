@@ -1,0 +1,450 @@
+// Forward kernel: O = softmax(Q K^T * scale [+causal]) V and LSE for head_dim 512 on sm_100a.
+//
+// A 128 x 512 fp32 output tile fills all 512 TMEM columns of one SM, so a tile of 128 packed query
+// rows is split over a CTA PAIR and every GEMM is a cta_group::2 UMMA with M = 128 (64 rows per
+// CTA). In that shape each CTA's 64 x N accumulator uses all 128 TMEM lanes with N/2 columns
+// (lanes 0-63 hold columns [0,N/2), lanes 64-127 hold [N/2,N)), so per CTA
+//     O (64 x 512)           -> 2 accumulators x 128 columns   = columns [0,256)
+//     S (64 x 256 keys) x 2  -> 2 buffers x 128 columns        = columns [256,512)
+// and the B operand of every MMA (K rows for QK^T, V columns for PV) is split between the two
+// CTAs, which halves the K/V bytes each SM pulls from L2.
+//
+// Per KV step of 256 keys:  S = Q K^T (32 MMAs, K-major operands)  ->  softmax warps: row max
+// (exchanged between the two threads that share a row), P = exp2(...) as bf16 into shared memory
+// -> O += P V (32 MMAs, V as MN-major B operand).  S is double buffered so the tensor pipe runs
+// S(j+1) while the softmax warps work on S(j).  O is only rescaled when a row max grows by more
+// than 2^8 (the exact value is restored by the final 1/rowsum scaling).
+//
+// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only) + TMEM
+// allocation, warps 4-7 softmax / epilogue. Follows the math of the reference forward
+// (src/flash_fwd_sm90_d512.py:921-1222, src/softmax.py:48-135) with a different decomposition.
+#include <cstring>
+
+#include "common.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace sd {
+
+namespace fwd {
+constexpr int kStepKeys = 256;                 // keys per KV step (UMMA N)
+constexpr int kStages = 8;                     // ring stages of 16 KB
+constexpr int kStageBytes = 16384;
+constexpr int kQBytes = kRowsPerCta * kHeadDim * 2;     // 64 KB
+constexpr int kPBytes = kRowsPerCta * kStepKeys * 2;    // 32 KB
+constexpr int kOffQ = 0;
+constexpr int kOffP = kOffQ + kQBytes;
+constexpr int kOffRing = kOffP + kPBytes;
+constexpr int kOffCtrl = kOffRing + kStages * kStageBytes;
+// control block layout (bytes from kOffCtrl)
+constexpr int kBarQFull = 0;
+constexpr int kBarFull = 8;                        // [kStages]
+constexpr int kBarEmpty = kBarFull + 8 * kStages;  // [kStages]
+constexpr int kBarSFull = kBarEmpty + 8 * kStages; // [2]
+constexpr int kBarPFull = kBarSFull + 16;
+constexpr int kBarPvDone = kBarPFull + 8;
+constexpr int kBarXchg = kBarPvDone + 8;           // [2] one per partner-warp pair
+constexpr int kTmemPtr = kBarXchg + 16;
+constexpr int kAbort = kTmemPtr + 4;
+constexpr int kXchg = 256;                         // float [2][128]
+constexpr int kCtrlBytes = kXchg + 2 * 128 * 4;
+constexpr int kSmemBytes = kOffCtrl + kCtrlBytes + 1024;  // + alignment slack
+constexpr int kTmemColsO = 0;
+constexpr int kTmemColsS = 256;
+constexpr float kRescaleThreshold = 8.0f;          // log2 units
+}  // namespace fwd
+
+template <bool kFp16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using namespace fwd;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base + kOffQ, sP = smem_base + kOffP, sRing = smem_base + kOffRing;
+  const uint32_t ctrl = smem_base + kOffCtrl;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
+  float* xchg = reinterpret_cast<float*>(smem + kOffCtrl + kXchg);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const TileGeom& g = p.g;
+
+  TileCoord tc;
+  const bool has_work = decode_tile(g, pair_id, tc);  // identical in both CTAs of the pair
+  if (!has_work) return;                              // uniform over the whole cluster
+
+  // number of KV steps this tile needs
+  int kv_hi = tc.sk;
+  if (g.causal) {
+    const int last_pos = min(tc.p0 + 2 * g.pos_per_cta, tc.sq) - 1;
+    kv_hi = min(kv_hi, last_pos + 1 + tc.sk - tc.sq);
+  }
+  const int n_steps = kv_hi > 0 ? (kv_hi + kStepKeys - 1) / kStepKeys : 0;
+
+  // ---------------------------------------------------------------- setup
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(ctrl + kBarQFull, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(ctrl + kBarFull + 8 * s, 1);
+      mbar_init(ctrl + kBarEmpty + 8 * s, 1);
+    }
+    mbar_init(ctrl + kBarSFull, 1);
+    mbar_init(ctrl + kBarSFull + 8, 1);
+    mbar_init(ctrl + kBarPFull, 8);   // 4 softmax warps x 2 CTAs
+    mbar_init(ctrl + kBarPvDone, 1);
+    mbar_init(ctrl + kBarXchg, 64);
+    mbar_init(ctrl + kBarXchg + 8, 64);
+    fence_mbar_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(ctrl + kTmemPtr, 512);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const uint32_t leader_q_full = mapa_u32(ctrl + kBarQFull, 0);
+  const uint32_t leader_p_full = mapa_u32(ctrl + kBarPFull, 0);
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_steps > 0) {
+      if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * kQBytes);
+      const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
+      const int qb = g.cu_q ? 0 : tc.b;
+      for (int d = 0; d < 8; ++d)
+        tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+
+      const int kb = g.cu_k ? 0 : tc.b;
+      uint32_t it = 0;
+      bool ok = true;
+      auto acquire = [&]() -> uint32_t {
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+        ok = ok && mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+        if (ok && rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+        ++it;
+        return s;
+      };
+      auto load_k = [&](int j) {
+        const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
+        for (int d = 0; d < 8 && ok; ++d) {
+          const uint32_t s = acquire();
+          if (!ok) break;
+          tma_load_4d_pair(sRing + s * kStageBytes, &tm_k, mapa_u32(ctrl + kBarFull + 8 * s, 0), d * 64, key0,
+                           tc.hkv, kb);
+        }
+      };
+      auto load_v = [&](int j) {
+        for (int c = 0; c < 8 && ok; ++c) {
+          const int kq = c >> 1, m = c & 1;
+          const uint32_t s = acquire();
+          if (!ok) break;
+          const int key0 = tc.k_off + j * kStepKeys + kq * 64;
+          const int dv0 = m * 256 + static_cast<int>(rank) * 128;
+          const uint32_t bar = mapa_u32(ctrl + kBarFull + 8 * s, 0);
+          tma_load_4d_pair(sRing + s * kStageBytes, &tm_v, bar, dv0, key0, tc.hkv, kb);
+          tma_load_4d_pair(sRing + s * kStageBytes + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+        }
+      };
+      if (n_steps > 0) load_k(0);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        if (j + 1 < n_steps) load_k(j + 1);
+        load_v(j);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA)
+    if (rank == 0 && lane == 0 && n_steps > 0) {
+      constexpr uint32_t idesc_s = make_idesc(kFp16, false, false, 128, kStepKeys);
+      constexpr uint32_t idesc_pv = make_idesc(kFp16, false, true, 128, 256);
+      uint32_t it = 0;
+      bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      auto issue_s = [&](int j) {
+        const uint32_t d_tmem = tmem_base + kTmemColsS + (j & 1) * 128;
+        for (int d = 0; d < 8 && ok; ++d) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_desc_sw128(sQ + d * 8192 + k * 32, 16, 1024);
+            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 32, 16, 1024);
+            umma_ss<2>(d_tmem, da, db, idesc_s, (d | k) != 0);
+          }
+          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          ++it;
+        }
+        if (ok) umma_commit_pair(ctrl + kBarSFull + 8 * (j & 1), 3);
+      };
+      auto issue_pv = [&](int j) {
+        for (int c = 0; c < 8 && ok; ++c) {
+          const int kq = c >> 1, m = c & 1;
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + kTmemColsO + m * 128;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_desc_sw128(sP + kq * 8192 + k * 32, 16, 1024);
+            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 2048, 8192, 1024);
+            umma_ss<2>(d_tmem, da, db, idesc_pv, (j | kq | k) != 0);
+          }
+          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          ++it;
+        }
+        if (ok) umma_commit_pair(ctrl + kBarPvDone, 3);
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        if (j + 1 < n_steps) issue_s(j + 1);
+        if (!ok) break;
+        ok = mbar_wait<true>(ctrl + kBarPFull, j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_pv(j);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int q = warp & 3;
+    const int L = q * 32 + lane;            // TMEM lane of this thread
+    const int row = L & 63, half = L >> 6;  // row within the CTA, which half of the N columns
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t xbar = ctrl + kBarXchg + 8 * (q & 1);
+    const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
+    const int head = (g.pack_g > 1) ? tc.hu * g.pack_g + row % g.pack_g : tc.hu;
+    int limit = tc.sk - 1;                  // last visible key of this row
+    if (g.causal) limit = min(limit, pos + tc.sk - tc.sq);
+    const bool dump = (p.debug != nullptr) && pair_id == 0;
+
+    float m_ref = -INFINITY, l_sum = 0.f;
+    uint32_t xphase = 0;
+    bool ok = true;
+    uint32_t r[32];
+
+    for (int j = 0; j < n_steps && ok; ++j) {
+      ok = mbar_wait(ctrl + kBarSFull + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t s_addr = lane_addr + kTmemColsS + (j & 1) * 128;
+      const int key0 = j * kStepKeys + half * 128;  // key of this thread's column 0
+      const int cl = limit - key0;                   // columns > cl are masked
+      const bool masked = cl < 127;
+
+      // pass 1: row max over this thread's 128 columns
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        tmem_ld32(s_addr + c4 * 32, r);
+        tmem_ld_wait();
+        if (dump && j == 0) {
+          float* dst = p.debug + (static_cast<int>(rank) * 128 + L) * 128 + c4 * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(r[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]);
+          if (masked && (c4 * 32 + i > cl)) v = -INFINITY;
+          mx = fmaxf(mx, v);
+        }
+      }
+      // combine with the thread that holds the other half of this row
+      xchg[(j & 1) * 128 + L] = mx;
+      mbar_arrive(xbar);
+      ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+      ok = __all_sync(0xffffffffu, ok);
+      xphase ^= 1u;
+      if (!ok) break;
+      mx = fmaxf(mx, xchg[(j & 1) * 128 + (L ^ 64)]);
+
+      float factor = 1.f;
+      bool rescale = false;
+      if (m_ref == -INFINITY) {
+        m_ref = mx;
+      } else if ((mx - m_ref) * p.scale_log2 > kRescaleThreshold) {
+        factor = ex2((m_ref - mx) * p.scale_log2);
+        m_ref = mx;
+        l_sum *= factor;
+        rescale = true;
+      }
+      const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+
+      // pass 2: P = exp2(S * scale_log2 - ms), packed to 16 bit
+      uint32_t pk[64];
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        tmem_ld32(s_addr + c4 * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
+          float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
+          if (masked && (c4 * 32 + i > cl)) a = 0.f;
+          if (masked && (c4 * 32 + i + 1 > cl)) b = 0.f;
+          l_sum += a + b;
+          pk[c4 * 16 + (i >> 1)] = pack2<kFp16>(a, b);
+        }
+      }
+
+      // the P buffer and the O accumulators are free once PV(j-1) has completed
+      if (j > 0) {
+        ok = mbar_wait(ctrl + kBarPvDone, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+        for (int c8 = 0; c8 < 8; ++c8) {
+          tmem_ld32(lane_addr + kTmemColsO + c8 * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+          tmem_st32(lane_addr + kTmemColsO + c8 * 32, r);
+        }
+        tmem_st_wait();
+      }
+      // P row -> shared memory, K-major 128B-swizzled [64 rows][64 keys] blocks
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        const uint32_t blk = sP + (half * 2 + a) * 8192 + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t* w = &pk[a * 32 + c * 4];
+          st_shared_v4(blk + ((c ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_p_full);
+    }
+
+    // ---- epilogue
+    if (ok && n_steps > 0) {
+      ok = mbar_wait(ctrl + kBarPvDone, (n_steps - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after_sync();
+    }
+    if (ok) {
+      xchg[(n_steps & 1) * 128 + L] = l_sum;
+      mbar_arrive(xbar);
+      ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      const float l_tot = l_sum + xchg[(n_steps & 1) * 128 + (L ^ 64)];
+      const bool any = l_tot > 0.f;
+      const float inv = any ? 1.f / l_tot : 0.f;
+      const bool row_ok = pos < tc.sq;
+      if (row_ok && half == 0 && p.lse != nullptr) {
+        const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+        const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
+        const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + tc.q_off + pos
+                                   : (static_cast<int64_t>(tc.b) * g.heads_q + head) * tc.sq + pos;
+        p.lse[idx] = lse;
+      }
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b) +
+                       static_cast<int64_t>(tc.q_off + pos) * p.o_stride_s + static_cast<int64_t>(head) * p.o_stride_h;
+#pragma unroll 1
+      for (int c8 = 0; c8 < 8; ++c8) {
+        const int m = c8 >> 2, c4 = c8 & 3;
+        if (n_steps > 0) {
+          tmem_ld32(lane_addr + kTmemColsO + c8 * 32, r);
+          tmem_ld_wait();
+        }
+        if (dump) {
+          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + c8 * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(r[i]);
+        }
+        if (row_ok) {
+          uint16_t* dst = orow + m * 256 + half * 128 + c4 * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float a = any ? __uint_as_float(r[i + 2 * t]) * inv : 0.f;
+              const float b = any ? __uint_as_float(r[i + 2 * t + 1]) * inv : 0.f;
+              w[t] = pack2<kFp16>(a, b);
+            }
+            st_global_v4(dst + i, w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (dump) {
+        float* dst = p.debug + 32768 + 65536 + (static_cast<int>(rank) * 128 + L) * 2;
+        dst[0] = m_ref;
+        dst[1] = l_tot;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTA goes away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<2>(tmem_base, 512);
+  }
+}
+
+int launch_fwd(const splitd_params* p, cudaStream_t stream) {
+  FwdParams fp;
+  memset(&fp, 0, sizeof(fp));
+  fill_geom(p, fp.g);
+  const TileGeom& g = fp.g;
+  CUtensorMap tm_q, tm_k, tm_v;
+  if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, g.pos_per_cta, "q")) return e;
+  if (int e = make_kv_tmap(&tm_k, p->k, p, p->k_strides, 128, "k")) return e;
+  if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 64, "v")) return e;
+  if (reinterpret_cast<uintptr_t>(p->o) % 16 != 0 || p->o_strides[1] % 8 != 0 || p->o_strides[2] % 8 != 0 ||
+      p->o_strides[0] % 8 != 0)
+    return fail(SPLITD_ERR_INVALID_ARGUMENT, "o must be 16-byte aligned with strides that are multiples of 8 elements");
+  fp.o = p->o;
+  fp.lse = p->lse;
+  fp.o_stride_b = p->o_strides[0];
+  fp.o_stride_s = p->o_strides[1];
+  fp.o_stride_h = p->o_strides[2];
+  fp.total_q = p->total_q;
+  fp.scale_log2 = p->softmax_scale * kLog2e;
+  fp.status = p->status_flag;
+  fp.debug = p->debug;
+
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  const long long pairs = varlen ? static_cast<long long>(g.row_tiles) * g.head_units
+                                 : static_cast<long long>(g.row_tiles) * g.head_units * g.batch;
+  if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "forward grid out of range");
+  auto kern = p->dtype == SPLITD_DTYPE_FP16 ? splitd_fwd_kernel<true> : splitd_fwd_kernel<false>;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::kSmemBytes);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(ce));
+  kern<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(256), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(ce));
+  return 0;
+}
+
+}  // namespace sd

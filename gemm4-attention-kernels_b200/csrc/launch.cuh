@@ -1,0 +1,28 @@
+// Host-side launchers shared between the C-ABI file and the kernel translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "../../include/splitd_attn.h"
+#include "common.cuh"
+
+namespace sd {
+
+int fail(int code, const char* fmt, ...);
+int make_tmap(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
+              const uint32_t* box, const char* what);
+void fill_geom(const splitd_params* p, TileGeom& g);
+int make_q_tmap(CUtensorMap* map, const void* base, const splitd_params* p, const TileGeom& g, const int64_t* st,
+                int box_pos, const char* what);
+int make_kv_tmap(CUtensorMap* map, const void* base, const splitd_params* p, const int64_t* st, int box_rows,
+                 const char* what);
+
+int launch_fwd(const splitd_params* p, cudaStream_t stream);
+int launch_bwd_preprocess(const splitd_params* p, cudaStream_t stream);
+int launch_bwd_dq(const splitd_params* p, cudaStream_t stream);
+int launch_bwd_dkdv(const splitd_params* p, cudaStream_t stream);
+size_t bwd_rowstat_elems(const splitd_params* p);
+size_t bwd_workspace_bytes(const splitd_params* p);
+
+}  // namespace sd

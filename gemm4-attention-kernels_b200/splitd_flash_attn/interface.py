@@ -1,0 +1,613 @@
+"""Public API of the B200 SplitD FlashAttention (head_dim == 512).
+
+Drop-in for ``splitd-flash-attn/src/interface.py`` of cmriat/gemm4-attention-kernels: the two public
+functions keep the reference's signatures (interface.py:1226-1236, 1255-1271), argument meaning,
+return values, validation order and exception types; the kernels behind them are hand-written
+sm_100a CUDA reached through the C-ABI in ``include/splitd_attn.h``.
+
+Layouts: batched (B, S, H, 512); packed (T, H, 512) with int32 ``cu_seqlens`` of B+1 entries.
+LSE is fp32, (B, Hq, S) batched and (Hq, T) packed, natural log, -inf for rows without keys.
+Forward accepts bf16 and fp16; training (any input requiring grad) is bf16 only.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _capi
+
+SUPPORTED_HEAD_DIM = 512
+
+__all__ = ["split_flash_attn_func", "split_flash_attn_varlen_func"]
+
+
+# ---------------------------------------------------------------------------
+# validation (mirrors interface.py:79-261 of the reference)
+# ---------------------------------------------------------------------------
+
+
+def _validate_head_dims(head_dim: int, head_dim_v: int) -> None:
+    if head_dim != SUPPORTED_HEAD_DIM or head_dim_v != SUPPORTED_HEAD_DIM:
+        raise ValueError(
+            f"(head_dim, head_dim_v)=({head_dim}, {head_dim_v}) is not supported. "
+            f"This SplitD interface requires q/k head_dim == {SUPPORTED_HEAD_DIM} and "
+            f"v head_dim_v == {SUPPORTED_HEAD_DIM}."
+        )
+
+
+def _validate_tensor(tensor, name, expected_shape, expected_dtype, expected_device) -> None:
+    if tensor is None:
+        raise ValueError(f"{name} must not be None")
+    if tuple(tensor.shape) != tuple(expected_shape):
+        raise ValueError(f"{name} has shape {tuple(tensor.shape)}, expected {tuple(expected_shape)}")
+    if tensor.dtype != expected_dtype:
+        raise TypeError(f"{name} has dtype {tensor.dtype}, expected {expected_dtype}")
+    if tensor.device != expected_device:
+        raise RuntimeError(f"{name} is on {tensor.device}, expected {expected_device}")
+
+
+def _validate_device_arch(device: torch.device) -> None:
+    """Replaces ``_validate_sm90_arch`` (interface.py:123-130): this build needs sm_100."""
+    lib = _capi.load_library()
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    ok = lib.splitd_device_supported(index)
+    if ok != 1:
+        major, minor = torch.cuda.get_device_capability(index)
+        raise RuntimeError(
+            f"This SplitD interface requires Blackwell B200 (SM 10.x), got compute capability {major}.{minor}."
+        )
+
+
+def _validate_training_dtype(q, requires_grad: bool) -> None:
+    if requires_grad and q.dtype != torch.bfloat16:
+        raise NotImplementedError(
+            "SplitD training currently supports torch.bfloat16 only. "
+            f"Got q/k/v dtype {q.dtype}; use bfloat16 inputs or a different attention backend."
+        )
+
+
+def _validate_cu_seqlens(tensor, name, batch_size=None, total_tokens=None) -> None:
+    if tensor is None:
+        return
+    if tensor.ndim != 1:
+        raise ValueError(f"{name} must be a 1D tensor, got rank {tensor.ndim}")
+    if tensor.numel() == 0:
+        raise ValueError(f"{name} must have at least one element")
+    if batch_size is not None and tuple(tensor.shape) != (batch_size + 1,):
+        raise ValueError(f"{name} must have shape ({batch_size + 1},), got {tuple(tensor.shape)}")
+    if tensor.dtype != torch.int32:
+        raise TypeError(f"{name} must have dtype torch.int32, got {tensor.dtype}")
+    if tensor.stride(0) != 1:
+        raise ValueError(f"{name} must be contiguous")
+    if not tensor.is_cuda:
+        raise RuntimeError(f"{name} must be on a CUDA device, got {tensor.device}")
+    # one device->host copy for all value checks (the reference does three .item() syncs here)
+    host = tensor.detach().cpu()
+    first = int(host[0])
+    if first != 0:
+        raise ValueError(f"{name}[0] must be 0, got {first}")
+    if total_tokens is not None:
+        last = int(host[-1])
+        if last != total_tokens:
+            raise ValueError(f"{name}[-1] must equal total tokens ({total_tokens}), got {last}")
+    if host.numel() > 1 and bool(torch.any(host[1:] < host[:-1])):
+        raise ValueError(f"{name} must be monotonically non-decreasing")
+    return host
+
+
+def _validate_max_seqlen(host_cu, name, max_seqlen, max_name) -> None:
+    if host_cu is None:
+        return
+    if max_seqlen is None:
+        raise ValueError(f"{max_name} must be provided when {name} is provided")
+    if isinstance(max_seqlen, bool) or not isinstance(max_seqlen, int):
+        raise TypeError(f"{max_name} must be an int, got {type(max_seqlen).__name__}")
+    if max_seqlen < 0:
+        raise ValueError(f"{max_name} must be non-negative, got {max_seqlen}")
+    lengths = host_cu[1:] - host_cu[:-1]
+    actual_max = int(lengths.max()) if lengths.numel() > 0 else 0
+    if max_seqlen < actual_max:
+        raise ValueError(f"{max_name} ({max_seqlen}) must be >= max sequence length from {name} ({actual_max})")
+
+
+def _validate_qkv_common(q, k, v, cu_seqlens_q=None, cu_seqlens_k=None):
+    q_rank = 3 if cu_seqlens_q is not None else 4
+    kv_rank = 3 if cu_seqlens_k is not None else 4
+    if q.ndim != q_rank:
+        raise ValueError(f"q must have rank {q_rank}, got rank {q.ndim}")
+    if k.ndim != kv_rank:
+        raise ValueError(f"k must have rank {kv_rank}, got rank {k.ndim}")
+    if v.ndim != kv_rank:
+        raise ValueError(f"v must have rank {kv_rank}, got rank {v.ndim}")
+
+    num_head, head_dim = q.shape[-2:]
+    seqlen_k = k.shape[-3]
+    num_head_kv = k.shape[-2]
+    head_dim_v = v.shape[-1]
+    host_cu_q = host_cu_k = None
+
+    if cu_seqlens_q is None:
+        batch_size, seqlen_q = q.shape[:2]
+        total_q = batch_size * seqlen_q
+    else:
+        batch_size = cu_seqlens_q.numel() - 1
+        seqlen_q = None
+        total_q = q.shape[0]
+        host_cu_q = _validate_cu_seqlens(cu_seqlens_q, "cu_seqlens_q", batch_size, total_tokens=total_q)
+
+    if k.shape[-1] != head_dim:
+        raise ValueError(f"k head_dim is {k.shape[-1]}, expected {head_dim}")
+    if v.shape[-3] != seqlen_k or v.shape[-2] != num_head_kv:
+        raise ValueError(
+            f"v has shape {tuple(v.shape)}, expected matching seqlen/head dims (*, {seqlen_k}, {num_head_kv}, {head_dim_v})"
+        )
+    if cu_seqlens_k is None:
+        expected_k_shape = (batch_size, seqlen_k, num_head_kv, head_dim)
+        expected_v_shape = (batch_size, seqlen_k, num_head_kv, head_dim_v)
+    else:
+        host_cu_k = _validate_cu_seqlens(cu_seqlens_k, "cu_seqlens_k", batch_size, total_tokens=seqlen_k)
+        expected_k_shape = (seqlen_k, num_head_kv, head_dim)
+        expected_v_shape = (seqlen_k, num_head_kv, head_dim_v)
+    if tuple(k.shape) != expected_k_shape:
+        raise ValueError(f"k has shape {tuple(k.shape)}, expected {expected_k_shape}")
+    if tuple(v.shape) != expected_v_shape:
+        raise ValueError(f"v has shape {tuple(v.shape)}, expected {expected_v_shape}")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("SplitD inputs must be torch.float16 or torch.bfloat16")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise TypeError(f"q, k, and v must have the same dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+    for name, t in (("q", q), ("k", k), ("v", v), ("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k)):
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(f"{name} must be on a CUDA device, got {t.device}")
+    if num_head % num_head_kv != 0:
+        raise ValueError(f"num_head ({num_head}) must be divisible by num_head_kv ({num_head_kv})")
+    _validate_head_dims(head_dim, head_dim_v)
+    return batch_size, seqlen_q, total_q, seqlen_k, num_head, num_head_kv, host_cu_q, host_cu_k
+
+
+def _resolve_causal_local_window(causal, window_size_left, window_size_right):
+    """Same decision table as interface.py:297-318 (window (-1,-1) = full, (-1,0) = causal)."""
+    local = False
+    if window_size_left is not None or window_size_right is not None:
+        if causal:
+            raise ValueError("causal and window_size are mutually exclusive")
+        if window_size_left is not None and window_size_right is not None:
+            if window_size_left < 0 and window_size_right < 0:
+                causal, local = False, False
+            elif window_size_right == 0 and window_size_left < 0:
+                causal, local = True, False
+            else:
+                causal, local = False, True
+        else:
+            causal, local = False, True
+    return causal, local
+
+
+def _unsupported_features(requires_grad, softcap, local, score_mod=None, aux_tensors=None) -> None:
+    """Sliding-window and softcap are not built for sm_100a in either direction."""
+    unsupported = []
+    if softcap is not None and softcap != 0.0:
+        unsupported.append("softcap")
+    if local:
+        unsupported.append("local/window attention")
+    if score_mod is not None:
+        unsupported.append("score_mod")
+    if aux_tensors is not None:
+        unsupported.append("aux_tensors")
+    if unsupported:
+        what = "backward" if requires_grad else "B200 build"
+        raise NotImplementedError(f"SplitD {what} does not support " + ", ".join(unsupported) + ".")
+
+
+# ---------------------------------------------------------------------------
+# C-ABI plumbing
+# ---------------------------------------------------------------------------
+
+_status_flags: dict = {}
+
+
+def _status_flag(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    flag = _status_flags.get(key)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_flags[key] = flag
+    return flag
+
+
+def kernel_status(device: Optional[torch.device] = None) -> int:
+    """Synchronise and return the device status word (0 = no kernel gave up a bounded wait)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    return int(_status_flag(device).item())
+
+
+def _strides3(t: torch.Tensor, packed: bool):
+    if t.stride(-1) != 1:
+        raise ValueError("innermost (head_dim) stride must be 1")
+    if packed:
+        return (0, t.stride(0), t.stride(1))
+    return (t.stride(0), t.stride(1), t.stride(2))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _needs_copy(t: torch.Tensor) -> bool:
+    """TMA needs unit stride on D and 16-byte aligned outer strides; anything else is copied."""
+    if t.stride(-1) != 1 or t.data_ptr() % 16 != 0:
+        return True
+    return any(s % 8 != 0 for s in t.stride()[:-1])
+
+
+def _prep(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    return t.contiguous() if _needs_copy(t) else t
+
+
+def _fill_params(q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale, causal, debug=None) -> _capi.SplitdParams:
+    packed = cu_q is not None
+    p = _capi.SplitdParams()
+    p.q, p.k, p.v, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse)
+    p.cu_seqlens_q, p.cu_seqlens_k = _ptr(cu_q), _ptr(cu_k)
+    if packed:
+        p.batch = cu_q.numel() - 1
+        p.total_q, p.total_k = q.shape[0], k.shape[0]
+        p.max_seqlen_q, p.max_seqlen_k = int(max_q), int(max_k)
+    else:
+        p.batch, p.seqlen_q, p.seqlen_k = q.shape[0], q.shape[1], k.shape[1]
+    p.heads_q, p.heads_kv, p.head_dim = q.shape[-2], k.shape[-2], q.shape[-1]
+    p.q_strides[:] = _strides3(q, packed)
+    p.k_strides[:] = _strides3(k, packed)
+    p.v_strides[:] = _strides3(v, packed)
+    p.o_strides[:] = _strides3(out, packed)
+    p.softmax_scale = float(scale)
+    p.causal = 1 if causal else 0
+    p.dtype = _capi.SPLITD_DTYPE_FP16 if q.dtype == torch.float16 else _capi.SPLITD_DTYPE_BF16
+    p.status_flag = _ptr(_status_flag(q.device))
+    p.debug = _ptr(debug)
+    return p
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# ---------------------------------------------------------------------------
+# host wrappers (replace _flash_attn_fwd_sm90 / _flash_attn_bwd_sm90)
+# ---------------------------------------------------------------------------
+
+
+def _flash_attn_fwd(
+    q,
+    k,
+    v,
+    cu_seqlens_q=None,
+    cu_seqlens_k=None,
+    max_seqlen_q=None,
+    max_seqlen_k=None,
+    softmax_scale=None,
+    causal=False,
+    softcap=None,
+    window_size_left=None,
+    window_size_right=None,
+    pack_gqa=None,
+    return_lse=False,
+    out=None,
+    lse=None,
+    debug=None,
+):
+    """Forward host wrapper; same contract as ``_flash_attn_fwd_sm90`` (interface.py:362-554).
+
+    ``pack_gqa`` is accepted for compatibility: heads are always folded into rows when the group
+    size allows it, which gives identical results.
+    """
+    (batch_size, seqlen_q, total_q, seqlen_k, num_head, num_head_kv, host_cu_q, host_cu_k) = _validate_qkv_common(
+        q, k, v, cu_seqlens_q, cu_seqlens_k
+    )
+    requires_grad = q.requires_grad or k.requires_grad or v.requires_grad
+    _validate_training_dtype(q, requires_grad)
+    _validate_max_seqlen(host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
+    _validate_max_seqlen(host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
+    if (cu_seqlens_q is None) != (cu_seqlens_k is None):
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must be given together")
+    _validate_device_arch(q.device)
+    head_dim = q.shape[-1]
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(head_dim)
+    if softcap == 0.0:
+        softcap = None
+    causal, local = _resolve_causal_local_window(causal, window_size_left, window_size_right)
+    _unsupported_features(requires_grad, softcap, local)
+
+    q, k, v = (_prep(t.detach()) for t in (q, k, v))
+    device = q.device
+    q_lead = (batch_size, seqlen_q) if cu_seqlens_q is None else (total_q,)
+    lse_shape = (batch_size, num_head, seqlen_q) if cu_seqlens_q is None else (num_head, total_q)
+    if out is None:
+        out = torch.empty(*q_lead, num_head, head_dim, dtype=q.dtype, device=device)
+    else:
+        _validate_tensor(out, "out", (*q_lead, num_head, head_dim), q.dtype, device)
+    if lse is None:
+        lse = torch.empty(lse_shape, dtype=torch.float32, device=device) if (requires_grad or return_lse) else None
+    else:
+        _validate_tensor(lse, "lse", lse_shape, torch.float32, device)
+
+    if total_q == 0 or k.shape[-3] == 0:
+        out.zero_()
+        if lse is not None:
+            lse.fill_(float("-inf"))
+        return out, lse
+
+    params = _fill_params(
+        q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, debug
+    )
+    with torch.cuda.device(device):
+        _capi.check(_capi.load_library().splitd_fwd(ctypes.byref(params), _stream_ptr(device)))
+    return out, lse
+
+
+def _flash_attn_bwd(
+    q,
+    k,
+    v,
+    out,
+    dout,
+    lse,
+    softmax_scale=None,
+    causal=False,
+    softcap=0.0,
+    window_size_left=None,
+    window_size_right=None,
+    cu_seqlens_q=None,
+    cu_seqlens_k=None,
+    max_seqlen_q=None,
+    max_seqlen_k=None,
+    dlse=None,
+):
+    """Backward host wrapper; same contract as ``_flash_attn_bwd_sm90`` (interface.py:652-888):
+    preprocess, dQ and dK/dV launches on the current stream, dq/dk/dv in the input dtype with
+    dk/dv already reduced over the query heads of each KV head."""
+    _validate_device_arch(q.device)
+    if softcap != 0.0:
+        raise NotImplementedError("SplitD backward does not support softcap yet")
+    causal, local = _resolve_causal_local_window(causal, window_size_left, window_size_right)
+    if local:
+        raise NotImplementedError("SplitD backward does not support local/window attention yet")
+    (batch_size, seqlen_q, total_q, seqlen_k, num_head, num_head_kv, host_cu_q, host_cu_k) = _validate_qkv_common(
+        q, k, v, cu_seqlens_q, cu_seqlens_k
+    )
+    _validate_max_seqlen(host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
+    _validate_max_seqlen(host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
+    if q.dtype == torch.float16:
+        raise NotImplementedError("SplitD backward currently supports bfloat16 only.")
+    device = q.device
+    head_dim = q.shape[-1]
+    if cu_seqlens_q is not None:
+        out_shape, lse_shape = (total_q, num_head, head_dim), (num_head, total_q)
+    else:
+        out_shape, lse_shape = (batch_size, seqlen_q, num_head, head_dim), (batch_size, num_head, seqlen_q)
+    _validate_tensor(out, "out", out_shape, q.dtype, device)
+    _validate_tensor(dout, "dout", out_shape, q.dtype, device)
+    _validate_tensor(lse, "lse", lse_shape, torch.float32, device)
+    if dlse is not None:
+        _validate_tensor(dlse, "dlse", lse_shape, torch.float32, device)
+        dlse = dlse.contiguous()
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(head_dim)
+
+    q, k, v, out, dout = (_prep(t.detach()) for t in (q, k, v, out, dout))
+    lse = lse.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if total_q == 0 or k.shape[-3] == 0:
+        return dq.zero_(), dk.zero_(), dv.zero_()
+
+    packed = cu_seqlens_q is not None
+    params = _fill_params(
+        q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal
+    )
+    params.dout, params.dlse = _ptr(dout), _ptr(dlse)
+    params.dq, params.dk, params.dv = _ptr(dq), _ptr(dk), _ptr(dv)
+    params.do_strides[:] = _strides3(dout, packed)
+    params.dq_strides[:] = _strides3(dq, packed)
+    params.dk_strides[:] = _strides3(dk, packed)
+    params.dv_strides[:] = _strides3(dv, packed)
+    lib = _capi.load_library()
+    n_stat = lib.splitd_bwd_rowstat_elems(ctypes.byref(params))
+    n_ws = lib.splitd_bwd_workspace_bytes(ctypes.byref(params))
+    dpsum = torch.empty(n_stat, dtype=torch.float32, device=device)
+    lse_log2 = torch.empty(n_stat, dtype=torch.float32, device=device)
+    workspace = torch.empty(n_ws, dtype=torch.uint8, device=device)
+    params.dpsum, params.lse_log2 = _ptr(dpsum), _ptr(lse_log2)
+    params.workspace, params.workspace_bytes = _ptr(workspace), n_ws
+    with torch.cuda.device(device):
+        _capi.check(lib.splitd_bwd(ctypes.byref(params), _stream_ptr(device)))
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------
+# autograd (FlashAttnFunc, interface.py:1117-1173; varlen op pair, interface.py:909-1109)
+# ---------------------------------------------------------------------------
+
+
+class FlashAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal, window_size, softcap, pack_gqa, return_lse):
+        out, lse = _flash_attn_fwd(
+            q,
+            k,
+            v,
+            softmax_scale=softmax_scale,
+            causal=causal,
+            window_size_left=window_size[0],
+            window_size_right=window_size[1],
+            softcap=softcap,
+            pack_gqa=pack_gqa,
+            return_lse=return_lse,
+        )
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.causal = causal
+        ctx.window_size = window_size
+        ctx.softcap = softcap
+        ctx.return_lse = return_lse
+        ctx.set_materialize_grads(False)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, dlse):
+        q, k, v, out, lse = ctx.saved_tensors
+        if not ctx.return_lse:
+            dlse = None
+        if dout is None:
+            dout = torch.zeros_like(out)
+        dq, dk, dv = _flash_attn_bwd(
+            q,
+            k,
+            v,
+            out,
+            dout,
+            lse,
+            ctx.softmax_scale,
+            ctx.causal,
+            ctx.softcap,
+            window_size_left=ctx.window_size[0],
+            window_size_right=ctx.window_size[1],
+            dlse=dlse,
+        )
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class FlashAttnVarlenFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(
+        ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, window_size, softcap
+    ):
+        out, lse = _flash_attn_fwd(
+            q,
+            k,
+            v,
+            cu_seqlens_q=cu_seqlens_q,
+            cu_seqlens_k=cu_seqlens_k,
+            max_seqlen_q=max_seqlen_q,
+            max_seqlen_k=max_seqlen_k,
+            softmax_scale=softmax_scale,
+            causal=causal,
+            window_size_left=window_size[0],
+            window_size_right=window_size[1],
+            softcap=softcap,
+            return_lse=True,
+        )
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k)
+        ctx.max_seqlen_q, ctx.max_seqlen_k = max_seqlen_q, max_seqlen_k
+        ctx.softmax_scale, ctx.causal = softmax_scale, causal
+        ctx.window_size, ctx.softcap = window_size, softcap
+        ctx.set_materialize_grads(False)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, dlse):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        if dout is None:
+            dout = torch.zeros_like(out)
+        dq, dk, dv = _flash_attn_bwd(
+            q,
+            k,
+            v,
+            out,
+            dout,
+            lse,
+            ctx.softmax_scale,
+            ctx.causal,
+            ctx.softcap,
+            window_size_left=ctx.window_size[0],
+            window_size_right=ctx.window_size[1],
+            cu_seqlens_q=cu_q,
+            cu_seqlens_k=cu_k,
+            max_seqlen_q=ctx.max_seqlen_q,
+            max_seqlen_k=ctx.max_seqlen_k,
+            dlse=dlse,
+        )
+        return (dq, dk, dv) + (None,) * 8
+
+
+# ---------------------------------------------------------------------------
+# public API
+# ---------------------------------------------------------------------------
+
+
+def split_flash_attn_func(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    window_size: Tuple[Optional[int], Optional[int]] = (None, None),
+    softcap: float = 0.0,
+    pack_gqa: Optional[bool] = None,
+    return_lse: bool = False,
+):
+    """Batched SplitD FlashAttention for D=512 (interface.py:1226-1252 of the reference).
+
+    q (B, Sq, Hq, 512), k/v (B, Sk, Hkv, 512) with Hq % Hkv == 0. Returns ``out`` or ``(out, lse)``.
+    Training requires bf16 q/k/v; fp16 is accepted only for no-grad forward.
+    """
+    out, lse = FlashAttnFunc.apply(q, k, v, softmax_scale, causal, window_size, softcap, pack_gqa, return_lse)
+    return (out, lse) if return_lse else out
+
+
+def split_flash_attn_varlen_func(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: Optional[torch.Tensor] = None,
+    cu_seqlens_k: Optional[torch.Tensor] = None,
+    max_seqlen_q: Optional[int] = None,
+    max_seqlen_k: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    window_size: Tuple[Optional[int], Optional[int]] = (None, None),
+    softcap: float = 0.0,
+    pack_gqa: Optional[bool] = None,
+    score_mod: Optional[Callable] = None,
+    aux_tensors: Optional[list] = None,
+    return_lse: bool = False,
+):
+    """Packed (varlen) SplitD FlashAttention for D=512 (interface.py:1255-1316 of the reference).
+
+    q (Tq, Hq, 512), k/v (Tk, Hkv, 512); ``cu_seqlens_q/k`` int32 CUDA tensors of B+1 entries and
+    ``max_seqlen_q/k`` are mandatory. Returns ``out`` or ``(out, lse)`` with lse (Hq, Tq).
+    """
+    if cu_seqlens_q is None or cu_seqlens_k is None:
+        raise ValueError("split_flash_attn_varlen_func requires cu_seqlens_q and cu_seqlens_k")
+    if max_seqlen_q is None:
+        raise ValueError("max_seqlen_q must be provided when cu_seqlens_q is provided")
+    if max_seqlen_k is None:
+        raise ValueError("max_seqlen_k must be provided when cu_seqlens_k is provided")
+    if score_mod is not None:
+        raise NotImplementedError("score_mod is not supported by the SplitD varlen path")
+    if aux_tensors is not None:
+        raise NotImplementedError("aux_tensors is not supported by the SplitD varlen path")
+    if not isinstance(window_size, tuple) or len(window_size) != 2:
+        raise TypeError("window_size must be a tuple of (left, right)")
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    out, lse = FlashAttnVarlenFunc.apply(
+        q,
+        k,
+        v,
+        cu_seqlens_q,
+        cu_seqlens_k,
+        max_seqlen_q,
+        max_seqlen_k,
+        float(softmax_scale),
+        causal,
+        window_size,
+        softcap,
+    )
+    return (out, lse) if return_lse else out

@@ -1,0 +1,134 @@
+/*
+ * C-ABI of the B200 (sm_100a) D=512 SplitD FlashAttention library (libsplitd_attn.so).
+ *
+ * These entry points are what a foreign-function binding for the reference's attention path
+ * would bind. The reference (cmriat/gemm4-attention-kernels, directory splitd-flash-attn/)
+ * reaches its kernels through TVM-FFI compiled functions that are called positionally from
+ * src/interface.py; each function below names the call it replaces.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; every pointer is DEVICE memory owned by the caller;
+ *  - the library never allocates or frees device memory, never synchronises, never throws;
+ *  - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream);
+ *  - return value: 0 on success, a negative splitd_status otherwise; a human readable message for
+ *    the last failure on the calling thread is available from splitd_last_error();
+ *  - head_dim is fixed to 512 for q, k and v (src/interface.py:79-87);
+ *  - tensors use the reference's layouts: batched (B, S, H, 512), packed (T, H, 512) with int32
+ *    cu_seqlens of B+1 entries (src/interface.py:1226-1316); the innermost (D) stride is 1 and
+ *    the remaining strides are given in ELEMENTS in the params struct;
+ *  - lse is fp32 (B, Hq, Sq) batched / (Hq, T) packed, natural log, -inf for rows without keys;
+ *  - causal masks are bottom-right aligned: key j is visible to query i iff j <= i + Sk - Sq
+ *    (tests/test_flash_fwd_splitd_sdpa.py:119-123).
+ */
+#ifndef SPLITD_ATTN_H_
+#define SPLITD_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  SPLITD_OK = 0,
+  SPLITD_ERR_INVALID_ARGUMENT = -1, /* NULL pointer, bad shape, Hq % Hkv != 0, head_dim != 512 ... */
+  SPLITD_ERR_UNSUPPORTED = -2,      /* e.g. fp16 backward (src/interface.py:704-707)              */
+  SPLITD_ERR_DEVICE = -3,           /* not a compute-capability 10.x device                       */
+  SPLITD_ERR_CUDA = -4,             /* a CUDA runtime / driver call failed                        */
+  SPLITD_ERR_WORKSPACE = -5         /* workspace missing or smaller than *_workspace_bytes()      */
+} splitd_status;
+
+enum { SPLITD_DTYPE_BF16 = 0, SPLITD_DTYPE_FP16 = 1 };
+
+typedef struct {
+  /* ---- forward operands ---- */
+  const void* q; /* (B,Sq,Hq,512) or (Tq,Hq,512)   */
+  const void* k; /* (B,Sk,Hkv,512) or (Tk,Hkv,512) */
+  const void* v;
+  void* o;    /* like q; written by forward, read by backward                */
+  float* lse; /* may be NULL in forward; required by backward                */
+
+  /* ---- backward operands (ignored by splitd_fwd) ---- */
+  const void* dout;  /* like o                                                    */
+  const float* dlse; /* gradient w.r.t. lse, may be NULL                          */
+  void* dq;          /* like q                                                    */
+  void* dk;          /* like k (already summed over the Hq/Hkv query heads)       */
+  void* dv;          /* like v                                                    */
+  float* dpsum;      /* fp32 scratch, splitd_bwd_rowstat_elems() elements          */
+  float* lse_log2;   /* fp32 scratch, same size                                   */
+  void* workspace;   /* bf16 P / dS tile scratch, splitd_bwd_workspace_bytes()     */
+  size_t workspace_bytes;
+
+  /* ---- packed (varlen) layout; both NULL selects the batched layout ---- */
+  const int32_t* cu_seqlens_q; /* device, B+1 entries */
+  const int32_t* cu_seqlens_k;
+
+  /* ---- sizes ---- */
+  int32_t batch;
+  int32_t seqlen_q, seqlen_k; /* batched: S; packed: ignored                              */
+  int32_t total_q, total_k;   /* packed: T; batched: ignored                              */
+  int32_t max_seqlen_q, max_seqlen_k; /* packed: upper bounds on the sequence lengths     */
+  int32_t heads_q, heads_kv, head_dim;
+
+  /* ---- strides in elements: {batch, sequence (token), head}; packed layout ignores [0] ---- */
+  int64_t q_strides[3], k_strides[3], v_strides[3], o_strides[3];
+  int64_t do_strides[3], dq_strides[3], dk_strides[3], dv_strides[3];
+
+  float softmax_scale; /* > 0 */
+  int32_t causal;      /* 0 / 1 */
+  int32_t dtype;       /* SPLITD_DTYPE_* of q, k, v, o, dout, dq, dk, dv */
+
+  /* device word; a kernel that gives up a bounded wait stores a positive code here (0 = fine). */
+  int32_t* status_flag; /* may be NULL */
+
+  /* optional fp32 device buffer receiving raw accumulator dumps of the first tile (tests only) */
+  float* debug;
+} splitd_params;
+
+/* 1 if `device` can run this library (compute capability 10.x), 0 if not, <0 on CUDA error.
+ * Replaces _validate_sm90_arch (src/interface.py:123-130). */
+int splitd_device_supported(int device);
+
+/* Forward: o = softmax(q k^T * scale [+ causal mask]) v, lse = logsumexp of the scaled scores.
+ * Replaces the compiled forward call `compile_cache[key](q,k,v,out,lse,scale,cu_q,cu_k,...)`
+ * (src/interface.py:538-553, kernel src/flash_fwd_sm90_d512.py). bf16 or fp16. */
+int splitd_fwd(const splitd_params* p, void* stream);
+
+/* Number of fp32 elements the caller must provide in each of `dpsum` and `lse_log2`
+ * (row statistics, padded per sequence; src/interface.py:747-753). */
+size_t splitd_bwd_rowstat_elems(const splitd_params* p);
+
+/* Bytes of `workspace` the backward needs for the given problem. */
+size_t splitd_bwd_workspace_bytes(const splitd_params* p);
+
+/* Backward step 1: dpsum = rowsum(o * dout) - dlse, lse_log2 = lse * log2(e).
+ * Replaces `_bwd_preprocess.compile_cache[key](out,dout,dpsum,lse,lse_log2,None,cu_q,None,dlse)`
+ * (src/interface.py:615-641, kernel src/flash_bwd_preprocess.py). */
+int splitd_bwd_preprocess(const splitd_params* p, void* stream);
+
+/* Backward step 2: dq. Replaces the dQ call `(q,k,v,dout,lse_log2,dpsum,dq,scale,cu_q,cu_k)`
+ * (src/interface.py:875-886, kernel src/fmha_dq_sm90_d512.py). Also leaves the bf16 P and dS
+ * tiles of every (query tile, key tile) pair in `workspace` for step 3. */
+int splitd_bwd_dq(const splitd_params* p, void* stream);
+
+/* Backward step 3: dk, dv, reduced over the Hq/Hkv query heads of each KV head.
+ * Replaces the dK/dV call `(q,k,v,dout,lse_log2,dpsum,dk,dv,scale,cu_q,cu_k)`
+ * (src/interface.py:862-874, kernel src/fmha_dkdv_sm90_d512.py). Must follow splitd_bwd_dq on
+ * the same stream with the same params. */
+int splitd_bwd_dkdv(const splitd_params* p, void* stream);
+
+/* All three backward steps in order on `stream` (what _flash_attn_bwd_sm90 does,
+ * src/interface.py:652-888). */
+int splitd_bwd(const splitd_params* p, void* stream);
+
+/* Message of the last failure on this thread ("" if none). */
+const char* splitd_last_error(void);
+
+/* Library version string. */
+const char* splitd_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPLITD_ATTN_H_ */
