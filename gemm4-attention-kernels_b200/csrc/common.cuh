@@ -42,12 +42,41 @@ struct FwdParams {
   float* debug;
 };
 
+// Backward workspace: per head unit two bf16 matrices (P, then dS) of ws_rows x ws_pitch, rows in
+// packed order (row tile * 128 + row in tile), keys of the row's own sequence along the pitch.
+struct BwdParams {
+  TileGeom g;
+  const float* lse;       // forward LSE (natural log)
+  const float* dlse;      // may be nullptr
+  float* dpsum;           // rowsum(dO*O) - dlse, same indexing as lse
+  float* lse_log2;        // lse * log2(e), same indexing as lse
+  const void* o;
+  const void* dout;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  int64_t do_stride_b, do_stride_s, do_stride_h;
+  int64_t dq_stride_b, dq_stride_s, dq_stride_h;
+  int64_t dk_stride_b, dk_stride_s, dk_stride_h;
+  int64_t dv_stride_b, dv_stride_s, dv_stride_h;
+  uint16_t* ws;           // workspace base
+  int64_t ws_rows;        // rows per head unit (total row tiles * 128)
+  int64_t ws_pitch;       // keys per row (max sequence length rounded up to 256)
+  int total_q, total_k;
+  int key_tiles;          // batched: key tiles (256 keys) per sequence; packed: upper bound over all
+  float scale_log2, scale;
+  int* status;
+};
+
 // Which tile does this CTA pair work on. Returns false when the pair has nothing to do.
 struct TileCoord {
   int b, hu, hkv;
   int p0;        // first position of the pair's tile (sequence-relative)
   int sq, sk;    // this sequence's lengths
   int q_off, k_off;  // token offsets of the sequence in the packed tensors (0 when batched)
+  int rt;            // row tile index inside the sequence (natural order)
+  int tile_global;   // row tile index over all sequences (rows of the backward workspace / 128)
 };
 
 __device__ __forceinline__ bool decode_tile(const TileGeom& g, int pair_id, TileCoord& t) {
@@ -64,6 +93,7 @@ __device__ __forceinline__ bool decode_tile(const TileGeom& g, int pair_id, Tile
     t.q_off = 0;
     t.k_off = 0;
     if (g.causal) rt = g.row_tiles - 1 - rt;  // heaviest tiles first
+    t.tile_global = b * g.row_tiles + rt;
   } else {
     hu = pair_id / g.row_tiles;
     int idx = pair_id - hu * g.row_tiles;
@@ -85,12 +115,14 @@ __device__ __forceinline__ bool decode_tile(const TileGeom& g, int pair_id, Tile
     if (b < 0) return false;
     rt = idx - acc;
     if (g.causal) rt = nt - 1 - rt;
+    t.tile_global = acc + rt;
     t.k_off = g.cu_k[b];
     t.sk = g.cu_k[b + 1] - t.k_off;
   }
   t.b = b;
   t.hu = hu;
   t.hkv = (g.pack_g == g.group) ? hu : hu / g.group;  // folded: hu is the KV head already
+  t.rt = rt;
   t.p0 = rt * pos_per_pair;
   return true;
 }

@@ -24,5 +24,7 @@ int launch_bwd_dq(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_dkdv(const splitd_params* p, cudaStream_t stream);
 size_t bwd_rowstat_elems(const splitd_params* p);
 size_t bwd_workspace_bytes(const splitd_params* p);
+int fill_bwd_params(const splitd_params* p, BwdParams& bp);
+int check_workspace(const splitd_params* p);
 
 }  // namespace sd
