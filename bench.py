@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the D=512 SplitD attention path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One STEP is one pass of the reference's benchmark sweep (scripts/bench_splitd_512_gqa_bs16k.py:51-60):
+bf16, Hq=32, Hkv=4, D=512, fixed B*S=16384 with (B,S) in {(16,1024),(8,2048),(4,4096),(2,8192),(1,16384)},
+causal and non-causal, forward and backward (backward = preprocess + dQ + dK/dV). Inputs are synthetic
+N(0,1) like the reference's own benchmark; every shape's operands (1.2 GB) exceed the 126 MB L2.
+FLOPs: 4*B*Hq*Sq*Sk*D (x0.5 causal) forward, 2.5x that backward (src/bench_utils.py:16-46, scripts/...:56).
+
+`value` is the aggregate fwd+bwd TFLOP/s over the whole sweep with operands resident in HBM; `e2e` is the
+same metric through the public API (split_flash_attn_func + autograd) with pinned HOST buffers, host->device
+copies of q,k,v,dO and device->host copies of out,dq,dk,dv inside the timed region.
+With N>1 (torchrun) every rank runs the same sweep on its own seed (weak scaling; no collective on the
+data path; NCCL only for the barrier and the max-over-ranks time).
+
+--impl reference times the reference's CPU path (its pure-PyTorch fp32 attention, restated in
+oracle/attention_oracle.py) on the host cores for the same metric on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "gemm4-attention-kernels_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+HQ, HKV, D = 32, 4, 512
+SWEEP = [(16, 1024), (8, 2048), (4, 4096), (2, 8192), (1, 16384)]
+METRIC = "D512 GQA attn fwd+bwd TFLOP/s (bf16, B*S=16K sweep)"
+
+
+def flops_fwd(B, S, causal):
+    return 4.0 * B * HQ * S * S * D * (0.5 if causal else 1.0)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            j = json.load(f)
+        return j.get("bf16_tflops", 1590.0), j.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                parts = [x.strip() for x in out.split(",")]
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+                for n, val in zip(names, parts[2:6]):
+                    if val.lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the reference's pure-PyTorch fp32 attention (oracle port) on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(repeat=1):
+    """fwd + bwd of (B=1,S=1024,Hq=32,Hkv=4) causal and non-causal in fp32 on the host. Returns
+    (flops, seconds)."""
+    from oracle import attention_oracle as O
+
+    gen = torch.Generator().manual_seed(0)
+    B, S = 1, 1024
+    q = torch.randn(B, S, HQ, D, generator=gen)
+    k = torch.randn(B, S, HKV, D, generator=gen)
+    v = torch.randn(B, S, HKV, D, generator=gen)
+    do = torch.randn(B, S, HQ, D, generator=gen)
+    fl, t0 = 0.0, time.perf_counter()
+    for _ in range(repeat):
+        for causal in (False, True):
+            O.attention_fwd(q, k, v, causal)
+            O.attention_bwd(q, k, v, do, causal)
+            fl += 3.5 * flops_fwd(B, S, causal)
+    return fl, time.perf_counter() - t0
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    for _ in range(args.warmup):
+        cpu_sample()
+    t0 = time.perf_counter()
+    fl = 0.0
+    for _ in range(args.steps):
+        f, _ = cpu_sample()
+        fl += f
+    dt = time.perf_counter() - t0
+    val = fl / dt / 1e12
+    sample = "per step: fp32 fwd+bwd of B=1,S=1024,Hq=32,Hkv=4,D=512, causal and non-causal (oracle port of the reference's PyTorch attention)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "D=512 GQA attention fwd+bwd, Hq=32 Hkv=4, B*S=16K sweep (bounded sample on host cores)"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    from splitd_flash_attn import interface as I
+    from splitd_flash_attn import sharding, split_flash_attn_func
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    n_tok = 16384
+    # one set of operands, re-viewed per (B, S): the values are i.i.d. so any reshape is a valid draw
+    q = torch.randn(n_tok, HQ, D, device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn(n_tok, HKV, D, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(n_tok, HKV, D, device=dev, generator=gen).to(torch.bfloat16)
+    do = torch.randn(n_tok, HQ, D, device=dev, generator=gen).to(torch.bfloat16)
+    cases = [(B, S, causal) for (B, S) in SWEEP for causal in (False, True)]
+    total_fwd = sum(flops_fwd(B, S, c) for B, S, c in cases)
+    total_flops = 3.5 * total_fwd
+
+    # per-kernel event times, accumulated over the timed steps
+    kt = {"fwd": 0.0, "bwd_preprocess": 0.0, "bwd_dq": 0.0, "bwd_dkdv": 0.0}
+    per_case = {}
+
+    def one_step(record):
+        launches = 0
+        for (B, S, causal) in cases:
+            qq, kk, vv, dd = q.view(B, S, HQ, D), k.view(B, S, HKV, D), v.view(B, S, HKV, D), do.view(B, S, HQ, D)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True)
+            evs = []
+            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs)
+            launches += 4
+            if record is not None:
+                record.append(((B, S, causal), [e0] + evs))
+        return launches
+
+    for _ in range(args.warmup):
+        one_step(None)
+    barrier()
+    records = []
+    with ClockSampler(local_rank) as clocks:
+        t_start = torch.cuda.Event(enable_timing=True)
+        t_end = torch.cuda.Event(enable_timing=True)
+        t_start.record()
+        launches = 0
+        for _ in range(args.steps):
+            launches += one_step(records)
+        t_end.record()
+        barrier()
+    elapsed_ms = sharding.max_over_ranks(t_start.elapsed_time(t_end), dev)
+    value = world * total_flops * args.steps / (elapsed_ms * 1e-3) / 1e12
+    if I.kernel_status(dev) != 0:
+        raise RuntimeError("a kernel gave up a bounded wait during the benchmark")
+
+    for key, evs in records:
+        names = ["fwd", "bwd_preprocess", "bwd_dq", "bwd_dkdv"]
+        ts = [evs[i].elapsed_time(evs[i + 1]) for i in range(4)]
+        for n, t in zip(names, ts):
+            kt[n] += t
+        c = per_case.setdefault(key, [0.0, 0.0, 0])
+        c[0] += ts[0]
+        c[1] += ts[1] + ts[2] + ts[3]
+        c[2] += 1
+    sweep = []
+    for (B, S, causal), (tf, tb, n) in per_case.items():
+        f = flops_fwd(B, S, causal)
+        sweep.append({"B": B, "S": S, "causal": causal, "fwd_ms": tf / n, "bwd_ms": tb / n,
+                      "fwd_tflops": f / (tf / n) / 1e9, "bwd_tflops": 2.5 * f / (tb / n) / 1e9})
+    n_steps = args.steps
+    fwd_tflops = total_fwd * n_steps / kt["fwd"] / 1e9
+    bwd_tflops = 2.5 * total_fwd * n_steps / (kt["bwd_preprocess"] + kt["bwd_dq"] + kt["bwd_dkdv"]) / 1e9
+
+    # ---- roofline of the dominant kernel (tensor bound); algorithmic FLOPs per launch:
+    #      fwd = F_fwd, dQ kernel = 1.5 F_fwd (S, dP, dQ GEMMs), dK/dV kernel = F_fwd (dV, dK GEMMs)
+    peak, peak_sus, peak_kind = load_peaks()
+    algo = {"fwd": total_fwd, "bwd_dq": 1.5 * total_fwd, "bwd_dkdv": total_fwd}
+    dom = max(algo, key=lambda n: kt[n])
+    achieved = algo[dom] * n_steps / kt[dom] / 1e9
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None, "peak_source": f"{peak_kind} bf16 burst",
+                "per_kernel_tflops": {n: algo[n] * n_steps / kt[n] / 1e9 for n in algo},
+                "per_kernel_ms_per_step": {n: kt[n] / n_steps for n in kt}}
+
+    # ---- end to end through the public API with host buffers
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+    hq_, hk_, hv_, hdo_ = pin(q), pin(k), pin(v), pin(do)
+    ho, hdq = torch.empty_like(hq_), torch.empty_like(hq_)
+    hdk, hdv = torch.empty_like(hk_), torch.empty_like(hk_)
+    h2d = (hq_.numel() + hk_.numel() + hv_.numel() + hdo_.numel()) * 2 * len(cases)
+    d2h = (ho.numel() + hdq.numel() + hdk.numel() + hdv.numel()) * 2 * len(cases)
+
+    def e2e_step():
+        for (B, S, causal) in cases:
+            dq_ = hq_.to(dev, non_blocking=True).view(B, S, HQ, D).requires_grad_(True)
+            dk_ = hk_.to(dev, non_blocking=True).view(B, S, HKV, D).requires_grad_(True)
+            dv_ = hv_.to(dev, non_blocking=True).view(B, S, HKV, D).requires_grad_(True)
+            dd_ = hdo_.to(dev, non_blocking=True).view(B, S, HQ, D)
+            out = split_flash_attn_func(dq_, dk_, dv_, causal=causal)
+            gq, gk, gv = torch.autograd.grad(out, (dq_, dk_, dv_), dd_)
+            ho.copy_(out.detach().view(n_tok, HQ, D), non_blocking=True)
+            hdq.copy_(gq.view(n_tok, HQ, D), non_blocking=True)
+            hdk.copy_(gk.view(n_tok, HKV, D), non_blocking=True)
+            hdv.copy_(gv.view(n_tok, HKV, D), non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = sharding.max_over_ranks(s0.elapsed_time(s1), dev)
+    e2e_val = world * total_flops * e2e_steps / (e2e_ms * 1e-3) / 1e12
+
+    cpu_baseline = None
+    if rank == 0 and world == 1:
+        fl, dt = cpu_sample()
+        cpu_baseline = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": "fp32 fwd+bwd of B=1,S=1024,Hq=32,Hkv=4,D=512, causal and non-causal, once (oracle port of the reference's PyTorch attention)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "fwd+bwd sweep: Hq=32 Hkv=4 D=512, (B,S) in (16,1024),(8,2048),(4,4096),(2,8192),(1,16384), causal and non-causal",
+                       "l2": "operands of every shape (1.2 GB) exceed the 126 MB L2", "per_rank": "same sweep, own seed"},
+            "fwd_tflops": fwd_tflops, "bwd_tflops": bwd_tflops,
+            "fwd_frac_of_peak": fwd_tflops / peak, "bwd_frac_of_peak": bwd_tflops / peak,
+            "frac_of_nominal_2250": {"fwd": fwd_tflops / 2250.0, "bwd": bwd_tflops / 2250.0},
+            "frac_of_sustained": {"fwd": fwd_tflops / peak_sus, "bwd": bwd_tflops / peak_sus},
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": launches, "clocks": clocks.summary(), "sweep": sweep,
+            "context_sm90_readme": {"fwd_tflops": 270, "bwd_tflops": 100},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

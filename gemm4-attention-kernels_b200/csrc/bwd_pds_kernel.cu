@@ -1,0 +1,271 @@
+// Backward step 2a: the P and dS tiles.  S = Q K^T, dP = dO V^T on the tensor cores, then
+//     P = exp2(S*scale*log2e - lse_log2),   dS = P * (dP - dpsum) * scale
+// (src/fmha_dq_sm90_d512.py:1040-1090 / src/fmha_dkdv_sm90_d512.py:1060-1130 of the reference) are written
+// as bf16 to the workspace, rows in packed order, so that dQ, dK and dV are three plain GEMMs over them
+// (bwd_grad_kernel.cu) and nothing is recomputed. The reference recomputes S and dP in each of four
+// D passes of both of its backward kernels (3.8x the useful FLOPs).
+//
+// Query-stationary CTA pair, cta_group::2 UMMAs with M = 128 (64 packed rows per CTA), N = 256 keys per
+// step. No accumulator lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns:
+// the tensor pipe fills one pair while eight element-wise warps drain the other. Q and dO (64 x 512 each)
+// stay in shared memory; K and V rows stream through a 6 x 16 KB ring.
+// A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
+// the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
+// fully masked and therefore zero.
+#include <cstring>
+
+#include "common.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace sd {
+
+namespace pds {
+constexpr int kStepKeys = 256;
+constexpr int kStages = 6;
+constexpr int kStageBytes = 16384;
+constexpr int kOffQ = 0;
+constexpr int kOffDO = 65536;
+constexpr int kOffRing = 131072;
+constexpr int kOffCtrl = kOffRing + kStages * kStageBytes;
+constexpr int kBarQFull = 0;
+constexpr int kBarFull = 8;
+constexpr int kBarEmpty = kBarFull + 8 * kStages;
+constexpr int kBarSdpFull = kBarEmpty + 8 * kStages;  // [2]
+constexpr int kBarSdpFree = kBarSdpFull + 16;         // [2], leader CTA only
+constexpr int kTmemPtr = kBarSdpFree + 16;
+constexpr int kAbort = kTmemPtr + 4;
+constexpr int kCtrlBytes = 256;
+constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
+}  // namespace pds
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
+splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const BwdParams p) {
+  using namespace pds;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw;
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_SMEM_ALIGN);
+    return;
+  }
+  const uint32_t sQ = smem_base + kOffQ, sDO = smem_base + kOffDO;
+  const uint32_t sRing = smem_base + kOffRing, ctrl = smem_base + kOffCtrl;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const TileGeom& g = p.g;
+
+  TileCoord tc;
+  if (!decode_tile(g, pair_id, tc)) return;
+
+  // key extent: that of the odd tile of this tile's pair (see header)
+  int kv_hi = tc.sk;
+  if (g.causal) {
+    const int ppp = 2 * g.pos_per_cta;
+    const int n_tiles = (tc.sq + ppp - 1) / ppp;
+    const int t_last = min(tc.rt | 1, n_tiles - 1);
+    const int last_pos = min((t_last + 1) * ppp, tc.sq) - 1;
+    kv_hi = min(kv_hi, last_pos + 1 + tc.sk - tc.sq);
+  }
+  const int n_steps = kv_hi > 0 ? (kv_hi + kStepKeys - 1) / kStepKeys : 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(ctrl + kBarQFull, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(ctrl + kBarFull + 8 * s, 1);
+      mbar_init(ctrl + kBarEmpty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(ctrl + kBarSdpFull + 8 * b, 1);
+      mbar_init(ctrl + kBarSdpFree + 8 * b, 16);  // 8 element-wise warps x 2 CTAs
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(ctrl + kTmemPtr, 512);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t leader_q_full = mapa_u32(ctrl + kBarQFull, 0);
+
+  if (warp == 0) {
+    if (lane == 0 && n_steps > 0) {
+      if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarQFull, 4 * 65536);
+      const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
+      const int qb = g.cu_q ? 0 : tc.b;
+      for (int d = 0; d < 8; ++d) {
+        tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+        tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+      }
+      const int kb = g.cu_k ? 0 : tc.b;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
+        for (int c = 0; c < 16 && ok; ++c) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          if (!ok) break;
+          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+          tma_load_4d_pair(sRing + s * kStageBytes, c < 8 ? &tm_k : &tm_v, mapa_u32(ctrl + kBarFull + 8 * s, 0),
+                           (c & 7) * 64, key0, tc.hkv, kb);
+          ++it;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && lane == 0 && n_steps > 0) {
+      constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
+      uint32_t it = 0;
+      bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      tc_fence_after_sync();
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int b = j & 1;
+        if (j >= 2) {  // buffer pair b must have been drained
+          ok = mbar_wait<true>(ctrl + kBarSdpFree + 8 * b, ((j >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        for (int c = 0; c < 16 && ok; ++c) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sA = (c < 8 ? sQ : sDO) + (c & 7) * 8192;
+          const uint32_t d_tmem = tmem_base + b * 256 + (c < 8 ? 0 : 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 32, 16, 1024);
+            umma_ss<2>(d_tmem, da, db, idesc, ((c & 7) | k) != 0);
+          }
+          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          ++it;
+        }
+        if (ok) umma_commit_pair(ctrl + kBarSdpFull + 8 * b, 3);
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3, wg = (warp - 4) >> 2;
+    const int L = q * 32 + lane;
+    const int row = L & 63, half = L >> 6;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
+    const int head = (g.pack_g > 1) ? tc.hu * g.pack_g + row % g.pack_g : tc.hu;
+    const bool row_ok = pos < tc.sq;
+    int limit = tc.sk - 1;
+    if (g.causal) limit = min(limit, pos + tc.sk - tc.sq);
+    if (!row_ok) limit = -1;
+    float lse2 = 0.f, delta = 0.f;
+    if (row_ok) {
+      const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + tc.q_off + pos
+                                 : (static_cast<int64_t>(tc.b) * g.heads_q + head) * tc.sq + pos;
+      lse2 = p.lse_log2[idx];
+      delta = p.dpsum[idx];
+    }
+    const int64_t plane = p.ws_rows * p.ws_pitch;
+    uint16_t* ws_p = p.ws + (static_cast<int64_t>(tc.hu) * 2) * plane +
+                     (static_cast<int64_t>(tc.tile_global) * kRowsPerPair + rank * kRowsPerCta + row) * p.ws_pitch;
+    uint16_t* ws_ds = ws_p + plane;
+    const uint32_t leader_free0 = mapa_u32(ctrl + kBarSdpFree, 0);
+
+    bool ok = true;
+    uint32_t s[64], d[32];
+    for (int j = 0; j < n_steps && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(ctrl + kBarSdpFull + 8 * b, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t s_addr = lane_addr + b * 256 + wg * 64;
+      const int key0 = j * kStepKeys + half * 128 + wg * 64;
+      const int cl = limit - key0;
+      tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_ld_wait();
+      // P (fp32, kept in s[]) with masked entries forced to zero
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float pv = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
+        s[i] = __float_as_uint(i > cl ? 0.f : pv);
+      }
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        tmem_ld32(s_addr + 128 + c2 * 32, d);
+        tmem_ld_wait();
+        if (c2 == 1) {  // both buffers of this step have been read: hand them back to the tensor pipe
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_free0 + 8 * b);
+        }
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = __uint_as_float(s[c2 * 32 + i]), p1 = __uint_as_float(s[c2 * 32 + i + 1]);
+          const float a = (c2 * 32 + i > cl) ? 0.f : p0 * (__uint_as_float(d[i]) - delta) * p.scale;
+          const float bb = (c2 * 32 + i + 1 > cl) ? 0.f : p1 * (__uint_as_float(d[i + 1]) - delta) * p.scale;
+          pk[i >> 1] = pack2<false>(p0, p1);
+          dk[i >> 1] = pack2<false>(a, bb);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          st_global_v4(ws_p + key0 + c2 * 32 + c * 8, pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+          st_global_v4(ws_ds + key0 + c2 * 32 + c * 8, dk[c * 4], dk[c * 4 + 1], dk[c * 4 + 2], dk[c * 4 + 3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<2>(tmem_base, 512);
+  }
+}
+
+int launch_bwd_pds(const splitd_params* p, cudaStream_t stream) {
+  BwdParams bp;
+  if (int e = fill_bwd_params(p, bp)) return e;
+  if (int e = check_workspace(p)) return e;
+  const TileGeom& g = bp.g;
+  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, g.pos_per_cta, "q")) return e;
+  if (int e = make_q_tmap(&tm_do, p->dout, p, g, p->do_strides, g.pos_per_cta, "dout")) return e;
+  if (int e = make_kv_tmap(&tm_k, p->k, p, p->k_strides, 128, "k")) return e;
+  if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 128, "v")) return e;
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  const long long pairs = varlen ? static_cast<long long>(g.row_tiles) * g.head_units
+                                 : static_cast<long long>(g.row_tiles) * g.head_units * g.batch;
+  if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "P/dS grid out of range");
+  cudaError_t ce =
+      cudaFuncSetAttribute(splitd_bwd_pds_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pds::kSmemBytes);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(pds): %s", cudaGetErrorString(ce));
+  splitd_bwd_pds_kernel<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(384), pds::kSmemBytes, stream>>>(
+      tm_q, tm_do, tm_k, tm_v, bp);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "P/dS launch failed: %s", cudaGetErrorString(ce));
+  return 0;
+}
+
+}  // namespace sd

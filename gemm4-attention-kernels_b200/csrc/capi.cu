@@ -192,8 +192,9 @@ int splitd_bwd_dkdv(const splitd_params* p, void* stream) {
 
 int splitd_bwd(const splitd_params* p, void* stream) {
   if (int e = splitd_bwd_preprocess(p, stream)) return e;
-  if (int e = splitd_bwd_dq(p, stream)) return e;
-  return splitd_bwd_dkdv(p, stream);
+  // P/dS tiles, then dQ, dK and dV as one GEMM launch (better tail behaviour than two launches)
+  if (int e = launch_bwd_pds(p, static_cast<cudaStream_t>(stream))) return e;
+  return launch_bwd_grad(p, static_cast<cudaStream_t>(stream), 3);
 }
 
 }  // extern "C"

@@ -15,8 +15,9 @@
 // S(j+1) while the softmax warps work on S(j).  O is only rescaled when a row max grows by more
 // than 2^8 (the exact value is restored by the final 1/rowsum scaling).
 //
-// Warp roles (256 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only) + TMEM
-// allocation, warps 4-7 softmax / epilogue. Follows the math of the reference forward
+// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only) + TMEM
+// allocation, warps 4-11 softmax / epilogue: two warps per TMEM lane quarter, each thread owning 64
+// of the 128 S columns of its lane, so a row of 256 keys is shared by four threads. Follows the math of the reference forward
 // (src/flash_fwd_sm90_d512.py:921-1222, src/softmax.py:48-135) with a different decomposition.
 #include <cstring>
 
@@ -46,22 +47,26 @@ constexpr int kBarPvDone = kBarPFull + 8;
 constexpr int kBarXchg = kBarPvDone + 8;           // [2] one per partner-warp pair
 constexpr int kTmemPtr = kBarXchg + 16;
 constexpr int kAbort = kTmemPtr + 4;
-constexpr int kXchg = 256;                         // float [2][128]
-constexpr int kCtrlBytes = kXchg + 2 * 128 * 4;
-constexpr int kSmemBytes = kOffCtrl + kCtrlBytes + 1024;  // + alignment slack
+constexpr int kXchg = 192;                         // float [2][256]
+constexpr int kCtrlBytes = kXchg + 2 * 256 * 4;
+constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;  // the dynamic segment is 1024-byte aligned (checked)
 constexpr int kTmemColsO = 0;
 constexpr int kTmemColsS = 256;
 constexpr float kRescaleThreshold = 8.0f;          // log2 units
 }  // namespace fwd
 
 template <bool kFp16>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
 splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using namespace fwd;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw;
+  if (smem_base & 1023u) {  // swizzled tiles need 1024-byte aligned bases
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_SMEM_ALIGN);
+    return;
+  }
   const uint32_t sQ = smem_base + kOffQ, sP = smem_base + kOffP, sRing = smem_base + kOffRing;
   const uint32_t ctrl = smem_base + kOffCtrl;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
@@ -95,10 +100,10 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     mbar_init(ctrl + kBarSFull, 1);
     mbar_init(ctrl + kBarSFull + 8, 1);
-    mbar_init(ctrl + kBarPFull, 8);   // 4 softmax warps x 2 CTAs
+    mbar_init(ctrl + kBarPFull, 16);  // 8 softmax warps x 2 CTAs
     mbar_init(ctrl + kBarPvDone, 1);
-    mbar_init(ctrl + kBarXchg, 64);
-    mbar_init(ctrl + kBarXchg + 8, 64);
+    mbar_init(ctrl + kBarXchg, 128);
+    mbar_init(ctrl + kBarXchg + 8, 128);
     fence_mbar_init();
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_k);
@@ -220,9 +225,10 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- softmax + epilogue
-    const int q = warp & 3;
+    const int q = warp & 3, wg = (warp - 4) >> 2;
     const int L = q * 32 + lane;            // TMEM lane of this thread
     const int row = L & 63, half = L >> 6;  // row within the CTA, which half of the N columns
+    const int xi = wg * 128 + L;            // slot in the exchange arrays
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t xbar = ctrl + kBarXchg + 8 * (q & 1);
     const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
@@ -234,44 +240,44 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float m_ref = -INFINITY, l_sum = 0.f;
     uint32_t xphase = 0;
     bool ok = true;
-    uint32_t r[32];
+    uint32_t r[64];
 
     for (int j = 0; j < n_steps && ok; ++j) {
       ok = mbar_wait(ctrl + kBarSFull + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t s_addr = lane_addr + kTmemColsS + (j & 1) * 128;
-      const int key0 = j * kStepKeys + half * 128;  // key of this thread's column 0
-      const int cl = limit - key0;                   // columns > cl are masked
-      const bool masked = cl < 127;
+      const uint32_t s_addr = lane_addr + kTmemColsS + (j & 1) * 128 + wg * 64;
+      const int key0 = j * kStepKeys + half * 128 + wg * 64;  // key of this thread's column 0
+      const int cl = limit - key0;                             // columns > cl are masked
+      const bool masked = cl < 63;
 
-      // pass 1: row max over this thread's 128 columns
-      float mx = -INFINITY;
+      tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      tmem_ld_wait();
+      if (dump && j == 0) {
+        float* dst = p.debug + (static_cast<int>(rank) * 128 + L) * 128 + wg * 64;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        tmem_ld32(s_addr + c4 * 32, r);
-        tmem_ld_wait();
-        if (dump && j == 0) {
-          float* dst = p.debug + (static_cast<int>(rank) * 128 + L) * 128 + c4 * 32;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(r[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (masked && (c4 * 32 + i > cl)) v = -INFINITY;
-          mx = fmaxf(mx, v);
-        }
+        for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(r[i]);
       }
-      // combine with the thread that holds the other half of this row
-      xchg[(j & 1) * 128 + L] = mx;
+      float mx = -INFINITY;
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i > cl) r[i] = 0xff800000u;  // -inf
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+
+      // combine with the three other threads that hold parts of this row
+      float* xs = xchg + (j & 1) * 256;
+      xs[xi] = mx;
       mbar_arrive(xbar);
       ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
       ok = __all_sync(0xffffffffu, ok);
       xphase ^= 1u;
       if (!ok) break;
-      mx = fmaxf(mx, xchg[(j & 1) * 128 + (L ^ 64)]);
+      mx = fmaxf(fmaxf(mx, xs[xi ^ 64]), fmaxf(xs[xi ^ 128], xs[xi ^ 192]));
 
       float factor = 1.f;
       bool rescale = false;
@@ -285,21 +291,13 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
 
-      // pass 2: P = exp2(S * scale_log2 - ms), packed to 16 bit
-      uint32_t pk[64];
+      // P = exp2(S * scale_log2 - ms), packed to 16 bit in place (masked entries are -inf -> 0)
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        tmem_ld32(s_addr + c4 * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
-          float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
-          if (masked && (c4 * 32 + i > cl)) a = 0.f;
-          if (masked && (c4 * 32 + i + 1 > cl)) b = 0.f;
-          l_sum += a + b;
-          pk[c4 * 16 + (i >> 1)] = pack2<kFp16>(a, b);
-        }
+      for (int i = 0; i < 64; i += 2) {
+        const float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
+        const float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
+        l_sum += a + b;
+        r[i >> 1] = pack2<kFp16>(a, b);
       }
 
       // the P buffer and the O accumulators are free once PV(j-1) has completed
@@ -310,25 +308,25 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after_sync();
       }
       if (__any_sync(0xffffffffu, rescale)) {
+        // this warp group rescales its half of the lane's 256 O columns
 #pragma unroll 1
-        for (int c8 = 0; c8 < 8; ++c8) {
-          tmem_ld32(lane_addr + kTmemColsO + c8 * 32, r);
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t t[32];
+          const uint32_t a = lane_addr + kTmemColsO + wg * 128 + c4 * 32;
+          tmem_ld32(a, t);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-          tmem_st32(lane_addr + kTmemColsO + c8 * 32, r);
+          for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
+          tmem_st32(a, t);
         }
         tmem_st_wait();
       }
-      // P row -> shared memory, K-major 128B-swizzled [64 rows][64 keys] blocks
+      // P row segment -> shared memory, K-major 128B-swizzled [64 rows][64 keys] blocks
+      {
+        const uint32_t blk = sP + (half * 2 + wg) * 8192 + row * 128;
 #pragma unroll
-      for (int a = 0; a < 2; ++a) {
-        const uint32_t blk = sP + (half * 2 + a) * 8192 + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t* w = &pk[a * 32 + c * 4];
-          st_shared_v4(blk + ((c ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
-        }
+        for (int c = 0; c < 8; ++c)
+          st_shared_v4(blk + ((c ^ (row & 7)) << 4), r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -342,18 +340,19 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
     }
+    float* xs = xchg + (n_steps & 1) * 256;
     if (ok) {
-      xchg[(n_steps & 1) * 128 + L] = l_sum;
+      xs[xi] = l_sum;
       mbar_arrive(xbar);
       ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      const float l_tot = l_sum + xchg[(n_steps & 1) * 128 + (L ^ 64)];
+      const float l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
       const bool any = l_tot > 0.f;
       const float inv = any ? 1.f / l_tot : 0.f;
       const bool row_ok = pos < tc.sq;
-      if (row_ok && half == 0 && p.lse != nullptr) {
+      if (row_ok && half == 0 && wg == 0 && p.lse != nullptr) {
         const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
         const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + tc.q_off + pos
@@ -362,34 +361,35 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b) +
                        static_cast<int64_t>(tc.q_off + pos) * p.o_stride_s + static_cast<int64_t>(head) * p.o_stride_h;
+      // warp group wg stores accumulator m = wg (dv columns [m*256 + half*128, +128))
 #pragma unroll 1
-      for (int c8 = 0; c8 < 8; ++c8) {
-        const int m = c8 >> 2, c4 = c8 & 3;
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t t[32];
         if (n_steps > 0) {
-          tmem_ld32(lane_addr + kTmemColsO + c8 * 32, r);
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c4 * 32, t);
           tmem_ld_wait();
         }
         if (dump) {
-          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + c8 * 32;
+          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + wg * 128 + c4 * 32;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(t[i]);
         }
         if (row_ok) {
-          uint16_t* dst = orow + m * 256 + half * 128 + c4 * 32;
+          uint16_t* dst = orow + wg * 256 + half * 128 + c4 * 32;
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint32_t w[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float a = any ? __uint_as_float(r[i + 2 * t]) * inv : 0.f;
-              const float b = any ? __uint_as_float(r[i + 2 * t + 1]) * inv : 0.f;
-              w[t] = pack2<kFp16>(a, b);
+            for (int u = 0; u < 4; ++u) {
+              const float a = any ? __uint_as_float(t[i + 2 * u]) * inv : 0.f;
+              const float b = any ? __uint_as_float(t[i + 2 * u + 1]) * inv : 0.f;
+              w[u] = pack2<kFp16>(a, b);
             }
             st_global_v4(dst + i, w[0], w[1], w[2], w[3]);
           }
         }
       }
-      if (dump) {
+      if (dump && wg == 0) {
         float* dst = p.debug + 32768 + 65536 + (static_cast<int>(rank) * 128 + L) * 2;
         dst[0] = m_ref;
         dst[1] = l_tot;
@@ -441,7 +441,7 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   auto kern = p->dtype == SPLITD_DTYPE_FP16 ? splitd_fwd_kernel<true> : splitd_fwd_kernel<false>;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::kSmemBytes);
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(ce));
-  kern<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(256), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
+  kern<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(384), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(ce));
   return 0;

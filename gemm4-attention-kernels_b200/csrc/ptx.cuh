@@ -19,6 +19,7 @@ enum : int {
   ST_TIMEOUT_MMA = 102,      // MMA issuer gave up waiting for operands
   ST_TIMEOUT_SOFTMAX = 103,  // softmax / epilogue warps gave up waiting for an accumulator
   ST_TIMEOUT_PEER = 104,
+  ST_BAD_SMEM_ALIGN = 105,   // dynamic shared memory not 1024-byte aligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

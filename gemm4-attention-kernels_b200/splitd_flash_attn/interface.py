@@ -369,6 +369,7 @@ def _flash_attn_bwd(
     max_seqlen_q=None,
     max_seqlen_k=None,
     dlse=None,
+    stage_events=None,
 ):
     """Backward host wrapper; same contract as ``_flash_attn_bwd_sm90`` (interface.py:652-888):
     preprocess, dQ and dK/dV launches on the current stream, dq/dk/dv in the input dtype with
@@ -426,7 +427,18 @@ def _flash_attn_bwd(
     params.dpsum, params.lse_log2 = _ptr(dpsum), _ptr(lse_log2)
     params.workspace, params.workspace_bytes = _ptr(workspace), n_ws
     with torch.cuda.device(device):
-        _capi.check(lib.splitd_bwd(ctypes.byref(params), _stream_ptr(device)))
+        if stage_events is None:
+            _capi.check(lib.splitd_bwd(ctypes.byref(params), _stream_ptr(device)))
+        else:
+            # same three launches, with a CUDA event before each and one after the last (profiling)
+            for fn in (lib.splitd_bwd_preprocess, lib.splitd_bwd_dq, lib.splitd_bwd_dkdv):
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                stage_events.append(ev)
+                _capi.check(fn(ctypes.byref(params), _stream_ptr(device)))
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            stage_events.append(ev)
     return dq, dk, dv
 
 

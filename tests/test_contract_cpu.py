@@ -1,0 +1,57 @@
+"""CPU: the parts of the public API contract that must fail before any CUDA work is attempted."""
+import pytest
+import torch
+
+D = 512
+
+
+def test_cpu_tensors_are_rejected_with_a_cuda_message():
+    # tests/test_flash_fwd_splitd_sdpa.py:400-406 of the reference
+    from splitd_flash_attn import split_flash_attn_func
+
+    q = torch.randn(1, 16, 2, D, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        split_flash_attn_func(q, q, q)
+
+
+def test_rank_and_dtype_errors():
+    from splitd_flash_attn import split_flash_attn_func, split_flash_attn_varlen_func
+
+    q = torch.randn(16, 2, D, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="rank 4"):
+        split_flash_attn_func(q, q, q)
+    q4 = torch.randn(1, 16, 2, D, dtype=torch.float32)
+    with pytest.raises(TypeError):
+        split_flash_attn_func(q4, q4, q4)
+    with pytest.raises(ValueError, match="cu_seqlens"):
+        split_flash_attn_varlen_func(q, q, q)
+    cu = torch.tensor([0, 16], dtype=torch.int32)
+    with pytest.raises(ValueError, match="max_seqlen_q"):
+        split_flash_attn_varlen_func(q, q, q, cu, cu, None, 16)
+    with pytest.raises(NotImplementedError):
+        split_flash_attn_varlen_func(q, q, q, cu, cu, 16, 16, score_mod=lambda *a: 0)
+    with pytest.raises(TypeError, match="tuple"):
+        split_flash_attn_varlen_func(q, q, q, cu, cu, 16, 16, window_size=[None, None])
+
+
+def test_window_resolution_table():
+    from splitd_flash_attn.interface import _resolve_causal_local_window as r
+
+    assert r(False, None, None) == (False, False)
+    assert r(True, None, None) == (True, False)
+    assert r(False, -1, -1) == (False, False)
+    assert r(False, -1, 0) == (True, False)
+    assert r(False, 16, 0) == (False, True)
+    assert r(False, 16, None) == (False, True)
+    with pytest.raises(ValueError):
+        r(True, 16, 0)
+
+
+def test_library_is_mandatory(monkeypatch):
+    """No CPU / PyTorch fallback: without the shared object the package refuses to run."""
+    from splitd_flash_attn import _capi
+
+    monkeypatch.setattr(_capi, "_lib", None)
+    monkeypatch.setattr(_capi, "LIB_PATH", "/nonexistent/libsplitd_attn.so")
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _capi.load_library()
