@@ -8,7 +8,8 @@
 // Query-stationary CTA pair, cta_group::2 UMMAs with M = 128 (64 packed rows per CTA), N = 256 keys per
 // step. No accumulator lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns:
 // the tensor pipe fills one pair while eight element-wise warps drain the other. Q and dO (64 x 512 each)
-// stay in shared memory; K and V rows stream through a 6 x 16 KB ring.
+// stay in shared memory; K and V rows stream through a 3 x 32 KB ring (8 MMAs per barrier round trip:
+// one thread issues a tcgen05.mma every ~45 cycles at best and each of these runs for 64).
 // A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
 // the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
 // fully masked and therefore zero.
@@ -22,8 +23,8 @@ namespace sd {
 
 namespace pds {
 constexpr int kStepKeys = 256;
-constexpr int kStages = 6;
-constexpr int kStageBytes = 16384;
+constexpr int kStages = 3;
+constexpr int kStageBytes = 32768;
 constexpr int kOffQ = 0;
 constexpr int kOffDO = 65536;
 constexpr int kOffRing = 131072;
@@ -117,13 +118,15 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       bool ok = true;
       for (int j = 0; j < n_steps && ok; ++j) {
         const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
-        for (int c = 0; c < 16 && ok; ++c) {
+        for (int c = 0; c < 8 && ok; ++c) {  // 4 stages of K then 4 of V, 128 of the 512 D columns each
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
           if (!ok) break;
           if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
-          tma_load_4d_pair(sRing + s * kStageBytes, c < 8 ? &tm_k : &tm_v, mapa_u32(ctrl + kBarFull + 8 * s, 0),
-                           (c & 7) * 64, key0, tc.hkv, kb);
+          const CUtensorMap* tm = c < 4 ? &tm_k : &tm_v;
+          const uint32_t bar = mapa_u32(ctrl + kBarFull + 8 * s, 0);
+          tma_load_4d_pair(sRing + s * kStageBytes, tm, bar, (2 * (c & 3)) * 64, key0, tc.hkv, kb);
+          tma_load_4d_pair(sRing + s * kStageBytes + 16384, tm, bar, (2 * (c & 3) + 1) * 64, key0, tc.hkv, kb);
           ++it;
         }
       }
@@ -131,6 +134,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   } else if (warp == 1) {
     if (rank == 0 && lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
+      const uint32_t q_lo = desc_lo(sQ, 16), do_lo = desc_lo(sDO, 16), ring_lo = desc_lo(sRing, 16);
       uint32_t it = 0;
       bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       tc_fence_after_sync();
@@ -141,18 +145,19 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (!ok) break;
           tc_fence_after_sync();
         }
-        for (int c = 0; c < 16 && ok; ++c) {
+#pragma unroll 1
+        for (int c = 0; c < 8 && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
           if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t sA = (c < 8 ? sQ : sDO) + (c & 7) * 8192;
-          const uint32_t d_tmem = tmem_base + b * 256 + (c < 8 ? 0 : 128);
+          const uint32_t a0 = (c < 4 ? q_lo : do_lo) + (c & 3) * (16384 >> 4);
+          const uint32_t b0 = ring_lo + s * (kStageBytes >> 4);
+          const uint32_t d_tmem = tmem_base + b * 256 + (c < 4 ? 0 : 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_desc_sw128(sA + k * 32, 16, 1024);
-            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 32, 16, 1024);
-            umma_ss<2>(d_tmem, da, db, idesc, ((c & 7) | k) != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;
+            const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;
+            umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc, ((c & 3) | k) != 0);
           }
           umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
           ++it;

@@ -101,7 +101,7 @@ int check_device() {
 }
 
 // Heads are folded into rows when the group size divides the 64 rows one CTA owns.
-void fill_geom(const splitd_params* p, TileGeom& g) {
+void fill_geom(const splitd_params* p, TileGeom& g, int rows_per_cta) {
   const bool varlen = p->cu_seqlens_q != nullptr;
   g.batch = p->batch;
   g.seqlen_q = varlen ? p->max_seqlen_q : p->seqlen_q;
@@ -111,7 +111,7 @@ void fill_geom(const splitd_params* p, TileGeom& g) {
   g.group = p->heads_q / p->heads_kv;
   g.pack_g = (g.group > 1 && g.group <= kRowsPerCta && kRowsPerCta % g.group == 0) ? g.group : 1;
   g.head_units = (g.pack_g == g.group) ? p->heads_kv : p->heads_q;
-  g.pos_per_cta = kRowsPerCta / g.pack_g;
+  g.pos_per_cta = rows_per_cta / g.pack_g;
   g.causal = p->causal ? 1 : 0;
   g.cu_q = p->cu_seqlens_q;
   g.cu_k = p->cu_seqlens_k;

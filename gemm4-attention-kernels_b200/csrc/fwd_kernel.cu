@@ -9,6 +9,7 @@
 // and the B operand of every MMA (K rows for QK^T, V columns for PV) is split between the two
 // CTAs, which halves the K/V bytes each SM pulls from L2.
 //
+// (Measured: this 64-rows-per-CTA form issues one 64 x 256 x 16 MMA per 64 cycles, i.e. full rate.)
 // Per KV step of 256 keys:  S = Q K^T (32 MMAs, K-major operands)  ->  softmax warps: row max
 // (exchanged between the two threads that share a row), P = exp2(...) as bf16 into shared memory
 // -> O += P V (32 MMAs, V as MN-major B operand).  S is double buffered so the tensor pipe runs
@@ -29,8 +30,8 @@ namespace sd {
 
 namespace fwd {
 constexpr int kStepKeys = 256;                 // keys per KV step (UMMA N)
-constexpr int kStages = 8;                     // ring stages of 16 KB
-constexpr int kStageBytes = 16384;
+constexpr int kStages = 4;                     // ring stages of 32 KB
+constexpr int kStageBytes = 32768;
 constexpr int kQBytes = kRowsPerCta * kHeadDim * 2;     // 64 KB
 constexpr int kPBytes = kRowsPerCta * kStepKeys * 2;    // 32 KB
 constexpr int kOffQ = 0;
@@ -78,6 +79,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int pair_id = blockIdx.x >> 1;
   const TileGeom& g = p.g;
 
+  // optional per-role cycle counters of one mid-grid pair (tests / tuning only)
+  const bool prof = p.debug != nullptr && pair_id == static_cast<int>(gridDim.x >> 2) && cluster_ctarank() == 0;
+  long long t_a = 0, t_b = 0, t_c = 0, t_all = 0;
   TileCoord tc;
   const bool has_work = decode_tile(g, pair_id, tc);  // identical in both CTAs of the pair
   if (!has_work) return;                              // uniform over the whole cluster
@@ -134,60 +138,84 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int kb = g.cu_k ? 0 : tc.b;
       uint32_t it = 0;
       bool ok = true;
-      auto acquire = [&]() -> uint32_t {
+      uint32_t full_bar[kStages];
+#pragma unroll
+      for (int s = 0; s < kStages; ++s) full_bar[s] = mapa_u32(ctrl + kBarFull + 8 * s, 0);
+      auto acquire = [&](uint32_t& st, uint32_t& bar) {
         const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+        const long long t0 = prof ? clock64() : 0;
         ok = ok && mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+        if (prof) t_a += clock64() - t0;
         if (ok && rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+        st = sRing + s * kStageBytes;
+        bar = full_bar[s];
         ++it;
-        return s;
       };
-      auto load_k = [&](int j) {
+      auto load_k = [&](int j) {  // this CTA's 128 key rows of the step, 128 of the 512 D columns per stage
         const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
-        for (int d = 0; d < 8 && ok; ++d) {
-          const uint32_t s = acquire();
+        for (int c = 0; c < 4 && ok; ++c) {
+          uint32_t st, bar;
+          acquire(st, bar);
           if (!ok) break;
-          tma_load_4d_pair(sRing + s * kStageBytes, &tm_k, mapa_u32(ctrl + kBarFull + 8 * s, 0), d * 64, key0,
-                           tc.hkv, kb);
+          tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
+          tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
         }
       };
-      auto load_v = [&](int j) {
-        for (int c = 0; c < 8 && ok; ++c) {
-          const int kq = c >> 1, m = c & 1;
-          const uint32_t s = acquire();
+      auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
+        for (int kq = 0; kq < 4 && ok; ++kq) {
+          uint32_t st, bar;
+          acquire(st, bar);
           if (!ok) break;
           const int key0 = tc.k_off + j * kStepKeys + kq * 64;
-          const int dv0 = m * 256 + static_cast<int>(rank) * 128;
-          const uint32_t bar = mapa_u32(ctrl + kBarFull + 8 * s, 0);
-          tma_load_4d_pair(sRing + s * kStageBytes, &tm_v, bar, dv0, key0, tc.hkv, kb);
-          tma_load_4d_pair(sRing + s * kStageBytes + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            const int dv0 = m * 256 + static_cast<int>(rank) * 128;
+            tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
+            tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+          }
         }
       };
-      if (n_steps > 0) load_k(0);
+      const long long tp0 = prof ? clock64() : 0;
+      load_k(0);
       for (int j = 0; j < n_steps && ok; ++j) {
         if (j + 1 < n_steps) load_k(j + 1);
         load_v(j);
       }
+      if (prof) {
+        p.debug[100000] = static_cast<float>(t_a);
+        p.debug[100001] = static_cast<float>(clock64() - tp0);
+        p.debug[100002] = static_cast<float>(n_steps);
+      }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA)
+    // One thread can issue a tcgen05.mma every ~45 cycles at best and each of these MMAs runs for 64, so
+    // the loop is kept to a few instructions per MMA: descriptor low words are advanced by adding, the
+    // high word is a constant, and one barrier wait / commit covers 8 MMAs (a 32 KB stage).
     if (rank == 0 && lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc_s = make_idesc(kFp16, false, false, 128, kStepKeys);
       constexpr uint32_t idesc_pv = make_idesc(kFp16, false, true, 128, 256);
+      const uint32_t q_lo = desc_lo(sQ, 16), p_lo = desc_lo(sP, 16);
+      const uint32_t ring_k_lo = desc_lo(sRing, 16), ring_v_lo = desc_lo(sRing, 8192);
       uint32_t it = 0;
+      t_all = prof ? clock64() : 0;
       bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       tc_fence_after_sync();
       auto issue_s = [&](int j) {
         const uint32_t d_tmem = tmem_base + kTmemColsS + (j & 1) * 128;
-        for (int d = 0; d < 8 && ok; ++d) {
+#pragma unroll 1
+        for (int c = 0; c < 4 && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_a += clock64() - t0;
           if (!ok) break;
-          tc_fence_after_sync();
+          const uint32_t a0 = q_lo + c * (16384 >> 4), b0 = ring_k_lo + s * (kStageBytes >> 4);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_desc_sw128(sQ + d * 8192 + k * 32, 16, 1024);
-            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 32, 16, 1024);
-            umma_ss<2>(d_tmem, da, db, idesc_s, (d | k) != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;      // A: 8 KB per 64-wide D block
+            const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;    // B: 16 KB per 64-wide D block
+            umma_ss<2>(d_tmem, desc_join(a0 + off), desc_join(b0 + offb), idesc_s, (c | k) != 0);
           }
           umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
           ++it;
@@ -195,32 +223,42 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (ok) umma_commit_pair(ctrl + kBarSFull + 8 * (j & 1), 3);
       };
       auto issue_pv = [&](int j) {
-        for (int c = 0; c < 8 && ok; ++c) {
-          const int kq = c >> 1, m = c & 1;
+#pragma unroll 1
+        for (int kq = 0; kq < 4 && ok; ++kq) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_b += clock64() - t0;
           if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + kTmemColsO + m * 128;
+          const uint32_t a0 = p_lo + kq * (8192 >> 4), b0 = ring_v_lo + s * (kStageBytes >> 4);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_desc_sw128(sP + kq * 8192 + k * 32, 16, 1024);
-            const uint64_t db = make_desc_sw128(sRing + s * kStageBytes + k * 2048, 8192, 1024);
-            umma_ss<2>(d_tmem, da, db, idesc_pv, (j | kq | k) != 0);
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+              umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
+                         desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
           }
           umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
           ++it;
         }
         if (ok) umma_commit_pair(ctrl + kBarPvDone, 3);
       };
-      if (ok) issue_s(0);
+      issue_s(0);
       for (int j = 0; j < n_steps && ok; ++j) {
         if (j + 1 < n_steps) issue_s(j + 1);
         if (!ok) break;
+        const long long t0 = prof ? clock64() : 0;
         ok = mbar_wait<true>(ctrl + kBarPFull, j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+        if (prof) t_c += clock64() - t0;
         if (!ok) break;
         tc_fence_after_sync();
         issue_pv(j);
+      }
+      if (prof) {
+        p.debug[100004] = static_cast<float>(t_a);
+        p.debug[100005] = static_cast<float>(t_b);
+        p.debug[100006] = static_cast<float>(t_c);
+        p.debug[100007] = static_cast<float>(clock64() - t_all);
       }
     }
   } else if (warp >= 4) {
@@ -243,7 +281,10 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint32_t r[64];
 
     for (int j = 0; j < n_steps && ok; ++j) {
+      long long t0 = prof ? clock64() : 0;
+      if (j == 0) t_all = t0;
       ok = mbar_wait(ctrl + kBarSFull + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+      if (prof) t_a += clock64() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -272,8 +313,10 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // combine with the three other threads that hold parts of this row
       float* xs = xchg + (j & 1) * 256;
       xs[xi] = mx;
+      t0 = prof ? clock64() : 0;
       mbar_arrive(xbar);
       ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+      if (prof) t_b += clock64() - t0;
       ok = __all_sync(0xffffffffu, ok);
       xphase ^= 1u;
       if (!ok) break;
@@ -302,7 +345,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
       // the P buffer and the O accumulators are free once PV(j-1) has completed
       if (j > 0) {
+        t0 = prof ? clock64() : 0;
         ok = mbar_wait(ctrl + kBarPvDone, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        if (prof) t_c += clock64() - t0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -334,6 +379,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (lane == 0) mbar_arrive_cluster(leader_p_full);
     }
 
+    if (prof && warp == 4 && lane == 0) {
+      p.debug[100008] = static_cast<float>(t_a);
+      p.debug[100009] = static_cast<float>(t_b);
+      p.debug[100010] = static_cast<float>(t_c);
+      p.debug[100011] = static_cast<float>(clock64() - t_all);
+    }
     // ---- epilogue
     if (ok && n_steps > 0) {
       ok = mbar_wait(ctrl + kBarPvDone, (n_steps - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);

@@ -12,7 +12,8 @@ namespace sd {
 int fail(int code, const char* fmt, ...);
 int make_tmap(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
               const uint32_t* box, const char* what);
-void fill_geom(const splitd_params* p, TileGeom& g);
+// rows_per_cta: packed query rows one CTA of a pair owns (64 or 128); heads fold when the group divides 64
+void fill_geom(const splitd_params* p, TileGeom& g, int rows_per_cta = kRowsPerCta);
 int make_q_tmap(CUtensorMap* map, const void* base, const splitd_params* p, const TileGeom& g, const int64_t* st,
                 int box_pos, const char* what);
 int make_kv_tmap(CUtensorMap* map, const void* base, const splitd_params* p, const int64_t* st, int box_rows,
