@@ -186,11 +186,10 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int64_t plane = p.ws_rows * p.ws_pitch;
     uint16_t* ws_p = p.ws + (static_cast<int64_t>(tc.hu) * 2) * plane +
                      (static_cast<int64_t>(tc.tile_global) * kRowsPerPair + rank * kRowsPerCta + row) * p.ws_pitch;
-    uint16_t* ws_ds = ws_p + plane;
     const uint32_t leader_free0 = mapa_u32(ctrl + kBarSdpFree, 0);
 
     bool ok = true;
-    uint32_t s[64], d[32];
+    uint32_t s[64], d[32];  // S / P of this thread's 64 keys; one 32-column slice of dP
     for (int j = 0; j < n_steps && ok; ++j) {
       const int b = j & 1;
       ok = mbar_wait(ctrl + kBarSdpFull + 8 * b, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
@@ -209,6 +208,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const float pv = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
         s[i] = __float_as_uint(i > cl ? 0.f : pv);
       }
+      uint32_t dk[32];
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {
         tmem_ld32(s_addr + 128 + c2 * 32, d);
@@ -218,20 +218,27 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(leader_free0 + 8 * b);
         }
-        uint32_t pk[16], dk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = __uint_as_float(s[c2 * 32 + i]), p1 = __uint_as_float(s[c2 * 32 + i + 1]);
           const float a = (c2 * 32 + i > cl) ? 0.f : p0 * (__uint_as_float(d[i]) - delta) * p.scale;
           const float bb = (c2 * 32 + i + 1 > cl) ? 0.f : p1 * (__uint_as_float(d[i + 1]) - delta) * p.scale;
-          pk[i >> 1] = pack2<false>(p0, p1);
-          dk[i >> 1] = pack2<false>(a, bb);
+          dk[c2 * 16 + (i >> 1)] = pack2<false>(a, bb);
         }
+      }
+      uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          st_global_v4(ws_p + key0 + c2 * 32 + c * 8, pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-          st_global_v4(ws_ds + key0 + c2 * 32 + c * 8, dk[c * 4], dk[c * 4 + 1], dk[c * 4 + 2], dk[c * 4 + 3]);
-        }
+      for (int i = 0; i < 64; i += 2) pk[i >> 1] = pack2<false>(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+      // 64 keys x 2 bytes = 8 chunks of 16 bytes per row; transpose so each store writes whole lines
+      transpose_chunks_8x8(pk, lane);
+      transpose_chunks_8x8(dk, lane);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        // this thread now holds chunk (lane & 7) of row (lane & ~7) + r; its own row is `lane`
+        const int64_t row_delta = static_cast<int64_t>((lane & ~7) + r - lane) * p.ws_pitch;
+        uint16_t* dst_p = ws_p + row_delta + key0 + (lane & 7) * 8;
+        st_global_v4(dst_p, pk[4 * r], pk[4 * r + 1], pk[4 * r + 2], pk[4 * r + 3]);
+        st_global_v4(dst_p + plane, dk[4 * r], dk[4 * r + 1], dk[4 * r + 2], dk[4 * r + 3]);
       }
     }
   }

@@ -64,7 +64,8 @@ static void ws_shape(const splitd_params* p, const TileGeom& g, int64_t& rows, i
   const bool varlen = p->cu_seqlens_q != nullptr;
   const int64_t tiles = varlen ? g.row_tiles : static_cast<int64_t>(g.row_tiles) * g.batch;
   rows = tiles * kRowsPerPair;
-  pitch = round_up(varlen ? p->max_seqlen_k : p->seqlen_k, 256);
+  // +64 elements (one 128-byte line) so consecutive rows do not sit a power of two apart in HBM
+  pitch = round_up(varlen ? p->max_seqlen_k : p->seqlen_k, 256) + 64;
 }
 
 size_t bwd_workspace_bytes(const splitd_params* p) {

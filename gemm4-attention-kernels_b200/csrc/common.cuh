@@ -62,7 +62,7 @@ struct BwdParams {
   int64_t dv_stride_b, dv_stride_s, dv_stride_h;
   uint16_t* ws;           // workspace base
   int64_t ws_rows;        // rows per head unit (total row tiles * 128)
-  int64_t ws_pitch;       // keys per row (max sequence length rounded up to 256)
+  int64_t ws_pitch;       // elements per row (max sequence length rounded up to 256, plus 64 of padding)
   int total_q, total_k;
   int key_tiles;          // batched: key tiles (256 keys) per sequence; packed: upper bound over all
   float scale_log2, scale;

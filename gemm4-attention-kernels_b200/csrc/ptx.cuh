@@ -368,4 +368,27 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// x holds 8 chunks of 16 bytes (4 words each) of ONE row per thread: x[4*c .. 4*c+3] = chunk c of row `lane`.
+// After the call, x[4*r .. 4*r+3] in lane l is chunk (l & 7) of row (lane & ~7) + r: an 8 x 8 transpose of
+// chunks inside every group of 8 lanes (3 butterfly rounds of warp shuffles). A store of word group r then
+// has 8 consecutive lanes writing one full 128-byte line, 4 lines per warp instruction instead of 32
+// partial ones.
+__device__ __forceinline__ void transpose_chunks_8x8(uint32_t (&x)[32], int lane) {
+#pragma unroll
+  for (int m = 1; m < 8; m <<= 1) {
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c & m) continue;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t a = x[4 * c + w], b = x[4 * (c | m) + w];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, up ? a : b, m);
+        x[4 * c + w] = up ? recv : a;
+        x[4 * (c | m) + w] = up ? b : recv;
+      }
+    }
+  }
+}
+
 }  // namespace sd
