@@ -25,6 +25,9 @@ EXPORTED_SYMBOLS = (
     "splitd_bwd_dq",
     "splitd_bwd_dkdv",
     "splitd_bwd",
+    "splitd_bwd_static_scratch",
+    "splitd_bwd_static_scratch_limit_rowstat",
+    "splitd_bwd_static_scratch_limit_workspace",
     "splitd_last_error",
     "splitd_version",
 )
@@ -99,13 +102,24 @@ def load_library() -> ctypes.CDLL:
     pp = ctypes.POINTER(SplitdParams)
     lib.splitd_device_supported.argtypes = [ctypes.c_int]
     lib.splitd_device_supported.restype = ctypes.c_int
-    for name in ("splitd_fwd", "splitd_bwd_preprocess", "splitd_bwd_dq", "splitd_bwd_dkdv", "splitd_bwd"):
+    for name in (
+        "splitd_fwd",
+        "splitd_bwd_preprocess",
+        "splitd_bwd_dq",
+        "splitd_bwd_dkdv",
+        "splitd_bwd",
+        "splitd_bwd_static_scratch",
+    ):
         fn = getattr(lib, name)
         fn.argtypes = [pp, ctypes.c_void_p]
         fn.restype = ctypes.c_int
     for name in ("splitd_bwd_rowstat_elems", "splitd_bwd_workspace_bytes"):
         fn = getattr(lib, name)
         fn.argtypes = [pp]
+        fn.restype = ctypes.c_size_t
+    for name in ("splitd_bwd_static_scratch_limit_rowstat", "splitd_bwd_static_scratch_limit_workspace"):
+        fn = getattr(lib, name)
+        fn.argtypes = []
         fn.restype = ctypes.c_size_t
     lib.splitd_last_error.restype = ctypes.c_char_p
     lib.splitd_version.restype = ctypes.c_char_p

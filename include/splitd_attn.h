@@ -122,6 +122,23 @@ int splitd_bwd_dkdv(const splitd_params* p, void* stream);
  * src/interface.py:652-888). */
 int splitd_bwd(const splitd_params* p, void* stream);
 
+/* Backward (all three steps, like splitd_bwd) that allocates NOTHING and needs no scratch from the caller.
+ * This entry point has no counterpart in the reference; it exists for callers that cannot call cudaMalloc:
+ * a latency-critical host thread that must stay off the allocator's locks, a plugin whose host framework owns
+ * all device memory and hands out only the tensors of the op, a process that was given a fixed memory budget. The scratch (dpsum, lse_log2 and
+ * the P/dS workspace; those three fields of `p` are ignored) is a 17 MiB array compiled into the library
+ * and resident on every GPU that loads it until the process exits.
+ *  - Limits: splitd_bwd_rowstat_elems(p) <= 65536 and splitd_bwd_workspace_bytes(p) <= 16 MiB
+ *    (e.g. B=1, S=512, Hq=8, Hkv=1). Larger problems return SPLITD_ERR_WORKSPACE with a message that says
+ *    which limit was hit; use splitd_bwd with your own buffers for those.
+ *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
+ *    device current). Make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents. Two calls that
+ *    overlap on the GPU (different streams, no dependency) race on it; order them yourself. */
+int splitd_bwd_static_scratch(const splitd_params* p, void* stream);
+size_t splitd_bwd_static_scratch_limit_rowstat(void);   /* 65536 floats   */
+size_t splitd_bwd_static_scratch_limit_workspace(void); /* 16 MiB         */
+
 /* Message of the last failure on this thread ("" if none). */
 const char* splitd_last_error(void);
 
