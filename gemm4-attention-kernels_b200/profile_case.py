@@ -1,0 +1,52 @@
+"""Run one shape of the attention path a few times and print CUDA-event timings per kernel.
+
+    python gemm4-attention-kernels_b200/profile_case.py --batch 1 --seqlen 4096 [--causal] [--no-backward] [--iters 3]
+
+Meant as the small, self-terminating command to put under `ncu` (one kernel, a few launches) and as a
+quick timing tool. Hq=32, Hkv=4, D=512, bf16, synthetic N(0,1) inputs (the benchmark's shapes).
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from splitd_flash_attn import interface as I  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--seqlen", type=int, default=4096)
+    ap.add_argument("--heads-q", type=int, default=32)
+    ap.add_argument("--heads-kv", type=int, default=4)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--no-backward", action="store_true")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    B, S, D = a.batch, a.seqlen, 512
+    mk = lambda h: torch.randn(B, S, h, D, device="cuda").to(torch.bfloat16)
+    q, k, v, do = mk(a.heads_q), mk(a.heads_kv), mk(a.heads_kv), mk(a.heads_q)
+    F = 4.0 * B * a.heads_q * S * S * D * (0.5 if a.causal else 1.0)
+    for it in range(a.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out, lse = I._flash_attn_fwd(q, k, v, causal=a.causal, return_lse=True)
+        e1.record()
+        evs = []
+        if not a.no_backward:
+            I._flash_attn_bwd(q, k, v, out, do, lse, causal=a.causal, stage_events=evs)
+        torch.cuda.synchronize()
+        line = f"iter {it}: fwd {e0.elapsed_time(e1):.3f} ms ({F / e0.elapsed_time(e1) / 1e9:.0f} TFLOP/s)"
+        if evs:
+            t = [evs[i].elapsed_time(evs[i + 1]) for i in range(3)]
+            line += (f" | preprocess {t[0]:.3f} ms | P/dS + dQ {t[1]:.3f} ms ({1.5 * F / t[1] / 1e9:.0f}) | "
+                     f"dK/dV {t[2]:.3f} ms ({F / t[2] / 1e9:.0f}) | bwd {2.5 * F / sum(t) / 1e9:.0f} TFLOP/s")
+        print(line)
+    print("status", I.kernel_status())
+
+
+if __name__ == "__main__":
+    main()
