@@ -62,6 +62,8 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int pair_id = blockIdx.x >> 1;
   const TileGeom& g = p.g;
 
+  const bool prof = p.debug != nullptr && pair_id == static_cast<int>(gridDim.x >> 2) && rank == 0;
+  long long t_a = 0, t_b = 0, t_c = 0, t_all = 0;
   TileCoord tc;
   if (!decode_tile(g, pair_id, tc)) return;
 
@@ -136,19 +138,24 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
       const uint32_t q_lo = desc_lo(sQ, 16), do_lo = desc_lo(sDO, 16), ring_lo = desc_lo(sRing, 16);
       uint32_t it = 0;
+      t_all = prof ? clock64() : 0;
       bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       tc_fence_after_sync();
       for (int j = 0; j < n_steps && ok; ++j) {
         const int b = j & 1;
         if (j >= 2) {  // buffer pair b must have been drained
+          const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait<true>(ctrl + kBarSdpFree + 8 * b, ((j >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_b += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
         }
 #pragma unroll 1
         for (int c = 0; c < 8 && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_a += clock64() - t0;
           if (!ok) break;
           const uint32_t a0 = (c < 4 ? q_lo : do_lo) + (c & 3) * (16384 >> 4);
           const uint32_t b0 = ring_lo + s * (kStageBytes >> 4);
@@ -163,6 +170,12 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           ++it;
         }
         if (ok) umma_commit_pair(ctrl + kBarSdpFull + 8 * b, 3);
+      }
+      if (prof) {
+        p.debug[0] = static_cast<float>(t_a);
+        p.debug[1] = static_cast<float>(t_b);
+        p.debug[2] = static_cast<float>(clock64() - t_all);
+        p.debug[3] = static_cast<float>(n_steps);
       }
     }
   } else if (warp >= 4) {
@@ -192,7 +205,10 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     uint32_t s[64], d[32];  // S / P of this thread's 64 keys; one 32-column slice of dP
     for (int j = 0; j < n_steps && ok; ++j) {
       const int b = j & 1;
+      const long long t0 = prof ? clock64() : 0;
+      if (j == 0) t_all = t0;
       ok = mbar_wait(ctrl + kBarSdpFull + 8 * b, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+      if (prof) t_c += clock64() - t0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -240,6 +256,10 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         st_global_v4(dst_p, pk[4 * r], pk[4 * r + 1], pk[4 * r + 2], pk[4 * r + 3]);
         st_global_v4(dst_p + plane, dk[4 * r], dk[4 * r + 1], dk[4 * r + 2], dk[4 * r + 3]);
       }
+    }
+    if (prof && warp == 4 && lane == 0) {
+      p.debug[4] = static_cast<float>(t_c);
+      p.debug[5] = static_cast<float>(clock64() - t_all);
     }
   }
 

@@ -112,6 +112,7 @@ int fill_bwd_params(const splitd_params* p, BwdParams& bp) {
   bp.scale = p->softmax_scale;
   bp.scale_log2 = p->softmax_scale * kLog2e;
   bp.status = p->status_flag;
+  bp.debug = p->debug;
   return 0;
 }
 

@@ -67,6 +67,7 @@ struct BwdParams {
   int key_tiles;          // batched: key tiles (256 keys) per sequence; packed: upper bound over all
   float scale_log2, scale;
   int* status;
+  float* debug;           // optional per-role cycle counters (tests / tuning only)
 };
 
 // Which tile does this CTA pair work on. Returns false when the pair has nothing to do.

@@ -370,6 +370,7 @@ def _flash_attn_bwd(
     max_seqlen_k=None,
     dlse=None,
     stage_events=None,
+    debug=None,
 ):
     """Backward host wrapper; same contract as ``_flash_attn_bwd_sm90`` (interface.py:652-888):
     preprocess, dQ and dK/dV launches on the current stream, dq/dk/dv in the input dtype with
@@ -413,6 +414,7 @@ def _flash_attn_bwd(
         q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal
     )
     params.dout, params.dlse = _ptr(dout), _ptr(dlse)
+    params.debug = _ptr(debug)
     params.dq, params.dk, params.dv = _ptr(dq), _ptr(dk), _ptr(dv)
     params.do_strides[:] = _strides3(dout, packed)
     params.dq_strides[:] = _strides3(dq, packed)
