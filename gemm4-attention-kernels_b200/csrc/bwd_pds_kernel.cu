@@ -196,6 +196,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       lse2 = p.lse_log2[idx];
       delta = p.dpsum[idx];
     }
+    const float nds = -delta * p.scale;
     const int64_t plane = p.ws_rows * p.ws_pitch;
     uint16_t* ws_p = p.ws + (static_cast<int64_t>(tc.hu) * 2) * plane +
                      (static_cast<int64_t>(tc.tile_global) * kRowsPerPair + rank * kRowsPerCta + row) * p.ws_pitch;
@@ -218,11 +219,17 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_ld_wait();
-      // P (fp32, kept in s[]) with masked entries forced to zero
+      // P (fp32, kept in s[]); masked entries are forced to zero (warp-uniform fast path without masks)
+      const bool full = __all_sync(0xffffffffu, cl >= 63);
+      if (full) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float pv = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
-        s[i] = __float_as_uint(i > cl ? 0.f : pv);
+        for (int i = 0; i < 64; ++i) s[i] = __float_as_uint(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2)));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float pv = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
+          s[i] = __float_as_uint(i > cl ? 0.f : pv);
+        }
       }
       uint32_t dk[32];
 #pragma unroll
@@ -234,12 +241,23 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(leader_free0 + 8 * b);
         }
+        // dS = P * (dP - delta) * scale = P * fma(dP, scale, -delta*scale); P is already 0 where masked,
+        // the select only guards against non-finite dP of rows/keys outside the sequence
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = __uint_as_float(s[c2 * 32 + i]), p1 = __uint_as_float(s[c2 * 32 + i + 1]);
-          const float a = (c2 * 32 + i > cl) ? 0.f : p0 * (__uint_as_float(d[i]) - delta) * p.scale;
-          const float bb = (c2 * 32 + i + 1 > cl) ? 0.f : p1 * (__uint_as_float(d[i + 1]) - delta) * p.scale;
-          dk[c2 * 16 + (i >> 1)] = pack2<false>(a, bb);
+          for (int i = 0; i < 32; i += 2) {
+            const float a = __uint_as_float(s[c2 * 32 + i]) * fmaf(__uint_as_float(d[i]), p.scale, nds);
+            const float bb = __uint_as_float(s[c2 * 32 + i + 1]) * fmaf(__uint_as_float(d[i + 1]), p.scale, nds);
+            dk[c2 * 16 + (i >> 1)] = pack2<false>(a, bb);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = __uint_as_float(s[c2 * 32 + i]), p1 = __uint_as_float(s[c2 * 32 + i + 1]);
+            const float a = (c2 * 32 + i > cl) ? 0.f : p0 * fmaf(__uint_as_float(d[i]), p.scale, nds);
+            const float bb = (c2 * 32 + i + 1 > cl) ? 0.f : p1 * fmaf(__uint_as_float(d[i + 1]), p.scale, nds);
+            dk[c2 * 16 + (i >> 1)] = pack2<false>(a, bb);
+          }
         }
       }
       uint32_t pk[32];

@@ -410,33 +410,42 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                    : (static_cast<int64_t>(tc.b) * g.heads_q + head) * tc.sq + pos;
         p.lse[idx] = lse;
       }
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b) +
-                       static_cast<int64_t>(tc.q_off + pos) * p.o_stride_s + static_cast<int64_t>(head) * p.o_stride_h;
-      // warp group wg stores accumulator m = wg (dv columns [m*256 + half*128, +128))
+      // Epilogue stores: each thread owns one row, so a plain 16-byte store per thread would touch 32
+      // different lines per warp instruction. 8 x 8 chunk transposes inside groups of 8 lanes make every
+      // store instruction write 4 full 128-byte lines instead.
+      uint16_t* obase = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b);
+      const int grp_row0 = row & ~7;  // first row of this lane's group of 8
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t t[32];
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t t[64];
         if (n_steps > 0) {
-          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c4 * 32, t);
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
           tmem_ld_wait();
         }
         if (dump) {
-          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + wg * 128 + c4 * 32;
+          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + wg * 128 + c2 * 64;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) dst[i] = __uint_as_float(t[i]);
+          for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(t[i]);
         }
-        if (row_ok) {
-          uint16_t* dst = orow + wg * 256 + half * 128 + c4 * 32;
+        uint32_t x[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
+        for (int i = 0; i < 64; i += 2) {
+          const float a = any ? __uint_as_float(t[i]) * inv : 0.f;
+          const float b = any ? __uint_as_float(t[i + 1]) * inv : 0.f;
+          x[i >> 1] = pack2<kFp16>(a, b);
+        }
+        transpose_chunks_8x8(x, lane);
+        // now x[4r..4r+3] = 16-byte chunk (lane & 7) of row grp_row0 + r
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float a = any ? __uint_as_float(t[i + 2 * u]) * inv : 0.f;
-              const float b = any ? __uint_as_float(t[i + 2 * u + 1]) * inv : 0.f;
-              w[u] = pack2<kFp16>(a, b);
-            }
-            st_global_v4(dst + i, w[0], w[1], w[2], w[3]);
+        for (int r = 0; r < 8; ++r) {
+          const int rr = grp_row0 + r;
+          const int pos_r = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + rr / g.pack_g;
+          const int head_r = (g.pack_g > 1) ? tc.hu * g.pack_g + rr % g.pack_g : tc.hu;
+          if (pos_r < tc.sq) {
+            uint16_t* dst = obase + static_cast<int64_t>(tc.q_off + pos_r) * p.o_stride_s +
+                            static_cast<int64_t>(head_r) * p.o_stride_h + wg * 256 + half * 128 + c2 * 64 + (lane & 7) * 8;
+            st_global_v4(dst, x[4 * r], x[4 * r + 1], x[4 * r + 2], x[4 * r + 3]);
           }
         }
       }
