@@ -190,6 +190,20 @@ int splitd_bwd_dkdv(const splitd_params* p, void* stream) {
   return launch_bwd_dkdv(p, static_cast<cudaStream_t>(stream));
 }
 
+int splitd_bwd_tiles(const splitd_params* p, void* stream) {
+  g_err[0] = 0;
+  if (int e = check_common(p, true)) return e;
+  if (int e = check_device()) return e;
+  return launch_bwd_pds(p, static_cast<cudaStream_t>(stream));
+}
+
+int splitd_bwd_grads(const splitd_params* p, void* stream) {
+  g_err[0] = 0;
+  if (int e = check_common(p, true)) return e;
+  if (int e = check_device()) return e;
+  return launch_bwd_grad(p, static_cast<cudaStream_t>(stream), 3);
+}
+
 int splitd_bwd(const splitd_params* p, void* stream) {
   if (int e = splitd_bwd_preprocess(p, stream)) return e;
   // P/dS tiles, then dQ, dK and dV as one GEMM launch (better tail behaviour than two launches)

@@ -42,8 +42,8 @@ def main():
         line = f"iter {it}: fwd {e0.elapsed_time(e1):.3f} ms ({F / e0.elapsed_time(e1) / 1e9:.0f} TFLOP/s)"
         if evs:
             t = [evs[i].elapsed_time(evs[i + 1]) for i in range(3)]
-            line += (f" | preprocess {t[0]:.3f} ms | P/dS + dQ {t[1]:.3f} ms ({1.5 * F / t[1] / 1e9:.0f}) | "
-                     f"dK/dV {t[2]:.3f} ms ({F / t[2] / 1e9:.0f}) | bwd {2.5 * F / sum(t) / 1e9:.0f} TFLOP/s")
+            line += (f" | preprocess {t[0]:.3f} ms | P/dS tiles {t[1]:.3f} ms ({F / t[1] / 1e9:.0f}) | "
+                     f"dQ+dK+dV GEMMs {t[2]:.3f} ms ({1.5 * F / t[2] / 1e9:.0f}) | bwd {2.5 * F / sum(t) / 1e9:.0f} TFLOP/s")
         print(line)
     print("status", I.kernel_status())
 

@@ -24,6 +24,8 @@ EXPORTED_SYMBOLS = (
     "splitd_bwd_preprocess",
     "splitd_bwd_dq",
     "splitd_bwd_dkdv",
+    "splitd_bwd_tiles",
+    "splitd_bwd_grads",
     "splitd_bwd",
     "splitd_bwd_static_scratch",
     "splitd_bwd_static_scratch_limit_rowstat",
@@ -107,6 +109,8 @@ def load_library() -> ctypes.CDLL:
         "splitd_bwd_preprocess",
         "splitd_bwd_dq",
         "splitd_bwd_dkdv",
+        "splitd_bwd_tiles",
+        "splitd_bwd_grads",
         "splitd_bwd",
         "splitd_bwd_static_scratch",
     ):

@@ -433,7 +433,8 @@ def _flash_attn_bwd(
             _capi.check(lib.splitd_bwd(ctypes.byref(params), _stream_ptr(device)))
         else:
             # same three launches, with a CUDA event before each and one after the last (profiling)
-            for fn in (lib.splitd_bwd_preprocess, lib.splitd_bwd_dq, lib.splitd_bwd_dkdv):
+            # (preprocess, P/dS tiles, gradient GEMMs: exactly the launches splitd_bwd makes)
+            for fn in (lib.splitd_bwd_preprocess, lib.splitd_bwd_tiles, lib.splitd_bwd_grads):
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record()
                 stage_events.append(ev)
