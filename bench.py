@@ -127,6 +127,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it can
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     cores = torch.get_num_threads()
     for _ in range(args.warmup):
         cpu_sample()
@@ -142,7 +144,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "D=512 GQA attention fwd+bwd, Hq=32 Hkv=4, B*S=16K sweep (bounded sample on host cores)"},
+        "config": {"workload": "fwd+bwd sweep: Hq=32 Hkv=4 D=512, (B,S) in (16,1024),(8,2048),(4,4096),(2,8192),(1,16384), causal and non-causal",
+                   "sample": "each step runs a bounded sample of that workload on the host cores: " + sample},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -165,6 +168,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("SPLITD_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
