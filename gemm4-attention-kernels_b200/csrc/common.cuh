@@ -37,7 +37,10 @@ struct FwdParams {
   float* lse;
   int64_t o_stride_b, o_stride_s, o_stride_h;  // elements
   int total_q;                                 // packed: T (lse row pitch)
-  float scale_log2;                            // softmax_scale * log2(e)
+  float scale_log2;                            // softmax_scale * log2(e); with softcap: softcap * log2(e)
+  float softcap_pre;                           // softmax_scale / softcap (0 = no softcap)
+  int win_left, win_right;                     // sliding window around the diagonal, -1 = unbounded
+  int total_pairs;                             // number of tile slots the persistent pairs walk over
   int* status;
   float* debug;
 };

@@ -8,17 +8,26 @@
 //     S (64 x 256 keys) x 2  -> 2 buffers x 128 columns        = columns [256,512)
 // and the B operand of every MMA (K rows for QK^T, V columns for PV) is split between the two
 // CTAs, which halves the K/V bytes each SM pulls from L2.
+// (Measured: this 64-rows-per-CTA form computes a 64 x 256 x 16 MMA in 64 cycles, i.e. full rate, but with
+// both operands in shared memory the operand fetch path (~68 B/clk/SM) makes it ~88 cycles.)
 //
-// (Measured: this 64-rows-per-CTA form issues one 64 x 256 x 16 MMA per 64 cycles, i.e. full rate.)
 // Per KV step of 256 keys:  S = Q K^T (32 MMAs, K-major operands)  ->  softmax warps: row max
-// (exchanged between the two threads that share a row), P = exp2(...) as bf16 into shared memory
+// (exchanged between the four threads that share a row), P = exp2(...) as bf16 into shared memory
 // -> O += P V (32 MMAs, V as MN-major B operand).  S is double buffered so the tensor pipe runs
 // S(j+1) while the softmax warps work on S(j).  O is only rescaled when a row max grows by more
 // than 2^8 (the exact value is restored by the final 1/rowsum scaling).
 //
+// PERSISTENT pairs: the grid is one pair per SM pair; each pair walks over tiles (snake order over the
+// tile list, which keeps pairs balanced under causal masking and keeps concurrently running pairs on the
+// same K/V). Shared memory is six 32 KB slots + a 32 KB P buffer: a tile's Q occupies two slots, the K/V
+// ring four. Q is loaded like any other ring entry, so the NEXT tile's Q arrives in the first two ring
+// slots that the current tile's last PV frees, and at the tile switch the old Q slots join the ring: no
+// idle time for launch, TMEM allocation, barrier set-up or the Q load between tiles, and the epilogue of
+// one tile overlaps the first two QK^T products of the next.
+//
 // Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only) + TMEM
 // allocation, warps 4-11 softmax / epilogue: two warps per TMEM lane quarter, each thread owning 64
-// of the 128 S columns of its lane, so a row of 256 keys is shared by four threads. Follows the math of the reference forward
+// of the 128 S columns of its lane. Follows the math of the reference forward
 // (src/flash_fwd_sm90_d512.py:921-1222, src/softmax.py:48-135) with a different decomposition.
 #include <cstring>
 
@@ -30,31 +39,62 @@ namespace sd {
 
 namespace fwd {
 constexpr int kStepKeys = 256;                 // keys per KV step (UMMA N)
-constexpr int kStages = 4;                     // ring stages of 32 KB
+constexpr int kStages = 4;                     // logical ring stages
+constexpr int kSlots = 6;                      // physical 32 KB slots: 4 ring + 2 Q
 constexpr int kStageBytes = 32768;
-constexpr int kQBytes = kRowsPerCta * kHeadDim * 2;     // 64 KB
-constexpr int kPBytes = kRowsPerCta * kStepKeys * 2;    // 32 KB
-constexpr int kOffQ = 0;
-constexpr int kOffP = kOffQ + kQBytes;
-constexpr int kOffRing = kOffP + kPBytes;
-constexpr int kOffCtrl = kOffRing + kStages * kStageBytes;
+constexpr int kOffSlots = 0;
+constexpr int kOffP = kSlots * kStageBytes;    // 32 KB P buffer
+constexpr int kOffCtrl = kOffP + 32768;
 // control block layout (bytes from kOffCtrl)
-constexpr int kBarQFull = 0;
-constexpr int kBarFull = 8;                        // [kStages]
+constexpr int kBarFull = 0;                        // [kStages]
 constexpr int kBarEmpty = kBarFull + 8 * kStages;  // [kStages]
 constexpr int kBarSFull = kBarEmpty + 8 * kStages; // [2]
 constexpr int kBarPFull = kBarSFull + 16;
 constexpr int kBarPvDone = kBarPFull + 8;
-constexpr int kBarXchg = kBarPvDone + 8;           // [2] one per partner-warp pair
+constexpr int kBarOFree = kBarPvDone + 8;
+constexpr int kBarXchg = kBarOFree + 8;            // [2] one per partner-warp set
 constexpr int kTmemPtr = kBarXchg + 16;
 constexpr int kAbort = kTmemPtr + 4;
 constexpr int kXchg = 192;                         // float [2][256]
 constexpr int kCtrlBytes = kXchg + 2 * 256 * 4;
 constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;  // the dynamic segment is 1024-byte aligned (checked)
+static_assert(kAbort + 4 <= kXchg, "control block overlap");
+static_assert(kSmemBytes <= 232448, "shared memory budget");
 constexpr int kTmemColsO = 0;
 constexpr int kTmemColsS = 256;
 constexpr float kRescaleThreshold = 8.0f;          // log2 units
 }  // namespace fwd
+
+// Slot tables kept in registers: nibble s of `tab` is the physical slot of logical ring stage s.
+__device__ __forceinline__ uint32_t slot_get(uint32_t tab, uint32_t s) { return (tab >> (4 * s)) & 15u; }
+__device__ __forceinline__ uint32_t slot_set(uint32_t tab, uint32_t s, uint32_t v) {
+  return (tab & ~(15u << (4 * s))) | (v << (4 * s));
+}
+
+// Tile slot visited by pair `pair` in round r (snake order). Returns false when the slot index is past
+// the end; `valid` says whether the slot holds a tile (the packed layout over-counts slots).
+__device__ __forceinline__ bool fwd_next_tile(const FwdParams& p, int r, int pair, int n_pairs, TileCoord& tc,
+                                              int& step0, int& n_steps, bool& valid) {
+  if (static_cast<long long>(r) * n_pairs >= p.total_pairs) return false;
+  const int idx = r * n_pairs + ((r & 1) ? n_pairs - 1 - pair : pair);
+  valid = idx < p.total_pairs && decode_tile(p.g, idx, tc);
+  step0 = 0;
+  n_steps = 0;
+  if (valid) {
+    // keys visible to row i: [i + sk - sq - win_left, i + sk - sq + win_right] (each side optional)
+    int kv_hi = tc.sk, kv_lo = 0;
+    if (p.win_right >= 0) {
+      const int last_pos = min(tc.p0 + 2 * p.g.pos_per_cta, tc.sq) - 1;
+      kv_hi = min(kv_hi, last_pos + 1 + tc.sk - tc.sq + p.win_right);
+    }
+    if (p.win_left >= 0) kv_lo = max(0, tc.p0 + tc.sk - tc.sq - p.win_left);
+    if (kv_hi > kv_lo) {
+      step0 = kv_lo / fwd::kStepKeys;
+      n_steps = (kv_hi + fwd::kStepKeys - 1) / fwd::kStepKeys - step0;
+    }
+  }
+  return true;
+}
 
 template <bool kFp16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
@@ -68,7 +108,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_SMEM_ALIGN);
     return;
   }
-  const uint32_t sQ = smem_base + kOffQ, sP = smem_base + kOffP, sRing = smem_base + kOffRing;
+  const uint32_t sSlots = smem_base + kOffSlots, sP = smem_base + kOffP;
   const uint32_t ctrl = smem_base + kOffCtrl;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
@@ -76,28 +116,16 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
-  const int pair_id = blockIdx.x >> 1;
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const TileGeom& g = p.g;
 
-  // optional per-role cycle counters of one mid-grid pair (tests / tuning only)
-  const bool prof = p.debug != nullptr && pair_id == static_cast<int>(gridDim.x >> 2) && cluster_ctarank() == 0;
+  // optional per-role cycle counters of pair 0 (tests / tuning only)
+  const bool prof = p.debug != nullptr && pair_id == 0 && rank == 0;
   long long t_a = 0, t_b = 0, t_c = 0, t_all = 0;
-  TileCoord tc;
-  const bool has_work = decode_tile(g, pair_id, tc);  // identical in both CTAs of the pair
-  if (!has_work) return;                              // uniform over the whole cluster
 
-  // number of KV steps this tile needs
-  int kv_hi = tc.sk;
-  if (g.causal) {
-    const int last_pos = min(tc.p0 + 2 * g.pos_per_cta, tc.sq) - 1;
-    kv_hi = min(kv_hi, last_pos + 1 + tc.sk - tc.sq);
-  }
-  const int n_steps = kv_hi > 0 ? (kv_hi + kStepKeys - 1) / kStepKeys : 0;
-
-  // ---------------------------------------------------------------- setup
+  // ---------------------------------------------------------------- setup (once per pair)
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(ctrl + kBarQFull, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(ctrl + kBarFull + 8 * s, 1);
       mbar_init(ctrl + kBarEmpty + 8 * s, 1);
@@ -106,6 +134,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(ctrl + kBarSFull + 8, 1);
     mbar_init(ctrl + kBarPFull, 16);  // 8 softmax warps x 2 CTAs
     mbar_init(ctrl + kBarPvDone, 1);
+    mbar_init(ctrl + kBarOFree, 16);
     mbar_init(ctrl + kBarXchg, 128);
     mbar_init(ctrl + kBarXchg + 8, 128);
     fence_mbar_init();
@@ -122,139 +151,186 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
-
-  const uint32_t leader_q_full = mapa_u32(ctrl + kBarQFull, 0);
   const uint32_t leader_p_full = mapa_u32(ctrl + kBarPFull, 0);
+  const uint32_t leader_o_free = mapa_u32(ctrl + kBarOFree, 0);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0 && n_steps > 0) {
-      if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * kQBytes);
-      const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
-      const int qb = g.cu_q ? 0 : tc.b;
-      for (int d = 0; d < 8; ++d)
-        tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
-
-      const int kb = g.cu_k ? 0 : tc.b;
-      uint32_t it = 0;
+    if (lane == 0) {
+      uint32_t it = 0;      // ring acquisitions so far (Q takes two per tile)
       bool ok = true;
-      uint32_t full_bar[kStages];
-#pragma unroll
-      for (int s = 0; s < kStages; ++s) full_bar[s] = mapa_u32(ctrl + kBarFull + 8 * s, 0);
-      auto acquire = [&](uint32_t& st, uint32_t& bar) {
+      uint32_t rs = 0x3210u;  // logical ring stage -> physical slot (one nibble each)
+      uint32_t qs = 0x54u;    // slots that held the previous tile's Q (free at the start)
+      const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0);
+      auto acquire = [&](uint32_t& st, uint32_t& bar, uint32_t& stage) {
         const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
         const long long t0 = prof ? clock64() : 0;
         ok = ok && mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
         if (prof) t_a += clock64() - t0;
         if (ok && rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
-        st = sRing + s * kStageBytes;
-        bar = full_bar[s];
+        st = sSlots + slot_get(rs, s) * kStageBytes;
+        bar = leader_full0 + 8 * s;
+        stage = s;
         ++it;
       };
-      auto load_k = [&](int j) {  // this CTA's 128 key rows of the step, 128 of the 512 D columns per stage
-        const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
-        for (int c = 0; c < 4 && ok; ++c) {
-          uint32_t st, bar;
-          acquire(st, bar);
-          if (!ok) break;
-          tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
-          tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
-        }
-      };
-      auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
-        for (int kq = 0; kq < 4 && ok; ++kq) {
-          uint32_t st, bar;
-          acquire(st, bar);
-          if (!ok) break;
-          const int key0 = tc.k_off + j * kStepKeys + kq * 64;
-#pragma unroll
-          for (int m = 0; m < 2; ++m) {
-            const int dv0 = m * 256 + static_cast<int>(rank) * 128;
-            tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
-            tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
-          }
-        }
-      };
+      TileCoord tc;
+      int step0, n_steps;
+      bool valid;
       const long long tp0 = prof ? clock64() : 0;
-      load_k(0);
-      for (int j = 0; j < n_steps && ok; ++j) {
-        if (j + 1 < n_steps) load_k(j + 1);
-        load_v(j);
+      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid); ++r) {
+        if (!valid || n_steps == 0) continue;
+        const int kb = g.cu_k ? 0 : tc.b;
+        // Q: two ring acquisitions (4 D blocks of 8 KB each) that stay resident for the whole tile
+        {
+          const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
+          const int qb = g.cu_q ? 0 : tc.b;
+          uint32_t newq = 0;
+          for (int u = 0; u < 2 && ok; ++u) {
+            uint32_t st, bar, stage;
+            acquire(st, bar, stage);
+            if (!ok) break;
+            for (int d = 0; d < 4; ++d)
+              tma_load_5d_pair(st + d * 8192, &tm_q, bar, (u * 4 + d) * 64, 0, qpos, tc.hu, qb);
+            newq = slot_set(newq, u, slot_get(rs, stage));
+            rs = slot_set(rs, stage, slot_get(qs, u));  // the previous tile's Q slot joins the ring here
+          }
+          qs = newq;
+        }
+        auto load_k = [&](int j) {  // this CTA's 128 key rows of the step, 128 of the 512 D columns per stage
+          const int key0 = tc.k_off + (step0 + j) * kStepKeys + static_cast<int>(rank) * 128;
+          for (int c = 0; c < 4 && ok; ++c) {
+            uint32_t st, bar, stage;
+            acquire(st, bar, stage);
+            if (!ok) break;
+            tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
+            tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
+          }
+        };
+        auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
+          for (int kq = 0; kq < 4 && ok; ++kq) {
+            uint32_t st, bar, stage;
+            acquire(st, bar, stage);
+            if (!ok) break;
+            const int key0 = tc.k_off + (step0 + j) * kStepKeys + kq * 64;
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+              const int dv0 = m * 256 + static_cast<int>(rank) * 128;
+              tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
+              tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+            }
+          }
+        };
+        load_k(0);
+        for (int j = 0; j < n_steps && ok; ++j) {
+          if (j + 1 < n_steps) load_k(j + 1);
+          load_v(j);
+        }
       }
       if (prof) {
         p.debug[100000] = static_cast<float>(t_a);
         p.debug[100001] = static_cast<float>(clock64() - tp0);
-        p.debug[100002] = static_cast<float>(n_steps);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA)
-    // One thread can issue a tcgen05.mma every ~45 cycles at best and each of these MMAs runs for 64, so
-    // the loop is kept to a few instructions per MMA: descriptor low words are advanced by adding, the
-    // high word is a constant, and one barrier wait / commit covers 8 MMAs (a 32 KB stage).
-    if (rank == 0 && lane == 0 && n_steps > 0) {
+    // One thread can issue a tcgen05.mma every ~45 cycles at best, so the loop is kept to a few
+    // instructions per MMA: descriptor low words are advanced by adding, the high word is a constant, and
+    // one barrier wait / commit covers 8 MMAs (a 32 KB stage).
+    if (rank == 0 && lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kFp16, false, false, 128, kStepKeys);
       constexpr uint32_t idesc_pv = make_idesc(kFp16, false, true, 128, 256);
-      const uint32_t q_lo = desc_lo(sQ, 16), p_lo = desc_lo(sP, 16);
-      const uint32_t ring_k_lo = desc_lo(sRing, 16), ring_v_lo = desc_lo(sRing, 8192);
-      uint32_t it = 0;
+      const uint32_t p_lo = desc_lo(sP, 16);
+      uint32_t it = 0;     // ring acquisitions consumed
+      uint32_t gs = 0;     // KV steps issued so far (S buffer / barrier phase index)
+      uint32_t tiles = 0;  // tiles with work done so far
+      uint32_t rs = 0x3210u, qs = 0x54u;  // same slot tables as the producer's
+      bool ok = true;
       t_all = prof ? clock64() : 0;
-      bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
-      tc_fence_after_sync();
-      auto issue_s = [&](int j) {
-        const uint32_t d_tmem = tmem_base + kTmemColsS + (j & 1) * 128;
-#pragma unroll 1
-        for (int c = 0; c < 4 && ok; ++c) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          const long long t0 = prof ? clock64() : 0;
-          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
-          if (prof) t_a += clock64() - t0;
-          if (!ok) break;
-          const uint32_t a0 = q_lo + c * (16384 >> 4), b0 = ring_k_lo + s * (kStageBytes >> 4);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t off = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;      // A: 8 KB per 64-wide D block
-            const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;    // B: 16 KB per 64-wide D block
-            umma_ss<2>(d_tmem, desc_join(a0 + off), desc_join(b0 + offb), idesc_s, (c | k) != 0);
+      TileCoord tc;
+      int step0, n_steps;
+      bool valid;
+      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid); ++r) {
+        if (!valid || n_steps == 0) continue;
+        // Q of this tile: wait for its two ring entries, hand the previous tile's Q slots to the ring
+        uint32_t q_lo[2];
+        {
+          uint32_t newq = 0;
+          for (int u = 0; u < 2 && ok; ++u) {
+            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            newq = slot_set(newq, u, slot_get(rs, s));
+            rs = slot_set(rs, s, slot_get(qs, u));
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);  // old Q slot is free once all earlier MMAs are done
+            ++it;
           }
-          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-          ++it;
-        }
-        if (ok) umma_commit_pair(ctrl + kBarSFull + 8 * (j & 1), 3);
-      };
-      auto issue_pv = [&](int j) {
-#pragma unroll 1
-        for (int kq = 0; kq < 4 && ok; ++kq) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          const long long t0 = prof ? clock64() : 0;
-          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
-          if (prof) t_b += clock64() - t0;
           if (!ok) break;
-          const uint32_t a0 = p_lo + kq * (8192 >> 4), b0 = ring_v_lo + s * (kStageBytes >> 4);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m)
-              umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
-                         desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
-          }
-          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-          ++it;
+          qs = newq;
+          q_lo[0] = desc_lo(sSlots + slot_get(qs, 0) * kStageBytes, 16);
+          q_lo[1] = desc_lo(sSlots + slot_get(qs, 1) * kStageBytes, 16);
         }
-        if (ok) umma_commit_pair(ctrl + kBarPvDone, 3);
-      };
-      issue_s(0);
-      for (int j = 0; j < n_steps && ok; ++j) {
-        if (j + 1 < n_steps) issue_s(j + 1);
-        if (!ok) break;
-        const long long t0 = prof ? clock64() : 0;
-        ok = mbar_wait<true>(ctrl + kBarPFull, j & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
-        if (prof) t_c += clock64() - t0;
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_pv(j);
+        auto issue_s = [&](uint32_t step) {
+          const uint32_t d_tmem = tmem_base + kTmemColsS + (step & 1) * 128;
+#pragma unroll 1
+          for (int c = 0; c < 4 && ok; ++c) {
+            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+            const long long t0 = prof ? clock64() : 0;
+            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            if (prof) t_a += clock64() - t0;
+            if (!ok) break;
+            const uint32_t a0 = (c < 2 ? q_lo[0] : q_lo[1]) + (((c & 1) * 16384) >> 4);
+            const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 16);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;   // A: 8 KB per 64-wide D block
+              const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;  // B: 16 KB per 64-wide D block
+              umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc_s, (c | k) != 0);
+            }
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            ++it;
+          }
+          if (ok) umma_commit_pair(ctrl + kBarSFull + 8 * (step & 1), 3);
+        };
+        auto issue_pv = [&](int j) {
+#pragma unroll 1
+          for (int kq = 0; kq < 4 && ok; ++kq) {
+            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+            const long long t0 = prof ? clock64() : 0;
+            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            if (prof) t_b += clock64() - t0;
+            if (!ok) break;
+            const uint32_t a0 = p_lo + kq * (8192 >> 4);
+            const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 8192);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+              for (int m = 0; m < 2; ++m)
+                umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
+                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
+            }
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            ++it;
+          }
+          if (ok) umma_commit_pair(ctrl + kBarPvDone, 3);
+        };
+        issue_s(gs);
+        for (int j = 0; j < n_steps && ok; ++j) {
+          if (j + 1 < n_steps) issue_s(gs + 1);
+          if (!ok) break;
+          const long long t0 = prof ? clock64() : 0;
+          ok = mbar_wait<true>(ctrl + kBarPFull, gs & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (ok && j == 0 && tiles > 0)  // the previous tile's epilogue must have drained O
+            ok = mbar_wait<true>(ctrl + kBarOFree, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_c += clock64() - t0;
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(j);
+          ++gs;
+        }
+        ++tiles;
       }
       if (prof) {
+        p.debug[100002] = static_cast<float>(gs);
         p.debug[100004] = static_cast<float>(t_a);
         p.debug[100005] = static_cast<float>(t_b);
         p.debug[100006] = static_cast<float>(t_c);
@@ -269,152 +345,160 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int xi = wg * 128 + L;            // slot in the exchange arrays
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t xbar = ctrl + kBarXchg + 8 * (q & 1);
-    const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
-    const int head = (g.pack_g > 1) ? tc.hu * g.pack_g + row % g.pack_g : tc.hu;
-    int limit = tc.sk - 1;                  // last visible key of this row
-    if (g.causal) limit = min(limit, pos + tc.sk - tc.sq);
-    const bool dump = (p.debug != nullptr) && pair_id == 0;
-
-    float m_ref = -INFINITY, l_sum = 0.f;
+    const int grp_row0 = row & ~7;          // first row of this lane's group of 8 (epilogue stores)
     uint32_t xphase = 0;
+    uint32_t gs = 0;                        // KV steps seen so far (same counter as the MMA issuer's)
     bool ok = true;
     uint32_t r[64];
+    TileCoord tc;
+    int step0, n_steps;
+    bool valid;
+    t_all = prof ? clock64() : 0;
 
-    for (int j = 0; j < n_steps && ok; ++j) {
-      long long t0 = prof ? clock64() : 0;
-      if (j == 0) t_all = t0;
-      ok = mbar_wait(ctrl + kBarSFull + 8 * (j & 1), (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-      if (prof) t_a += clock64() - t0;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t s_addr = lane_addr + kTmemColsS + (j & 1) * 128 + wg * 64;
-      const int key0 = j * kStepKeys + half * 128 + wg * 64;  // key of this thread's column 0
-      const int cl = limit - key0;                             // columns > cl are masked
-      const bool masked = cl < 63;
+    for (int rr = 0; ok && fwd_next_tile(p, rr, pair_id, n_pairs, tc, step0, n_steps, valid); ++rr) {
+      if (!valid) continue;
+      const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
+      const int head = (g.pack_g > 1) ? tc.hu * g.pack_g + row % g.pack_g : tc.hu;
+      int limit = tc.sk - 1;  // last visible key of this row
+      if (p.win_right >= 0) limit = min(limit, pos + tc.sk - tc.sq + p.win_right);
+      const int lo_limit = p.win_left >= 0 ? pos + tc.sk - tc.sq - p.win_left : 0;  // first visible key
+      float m_ref = -INFINITY, l_sum = 0.f;
 
-      tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-      tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-      tmem_ld_wait();
-      if (dump && j == 0) {
-        float* dst = p.debug + (static_cast<int>(rank) * 128 + L) * 128 + wg * 64;
-#pragma unroll
-        for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(r[i]);
-      }
-      float mx = -INFINITY;
-      if (masked) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i > cl) r[i] = 0xff800000u;  // -inf
-      }
-#pragma unroll
-      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-
-      // combine with the three other threads that hold parts of this row
-      float* xs = xchg + (j & 1) * 256;
-      xs[xi] = mx;
-      t0 = prof ? clock64() : 0;
-      mbar_arrive(xbar);
-      ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
-      if (prof) t_b += clock64() - t0;
-      ok = __all_sync(0xffffffffu, ok);
-      xphase ^= 1u;
-      if (!ok) break;
-      mx = fmaxf(fmaxf(mx, xs[xi ^ 64]), fmaxf(xs[xi ^ 128], xs[xi ^ 192]));
-
-      float factor = 1.f;
-      bool rescale = false;
-      if (m_ref == -INFINITY) {
-        m_ref = mx;
-      } else if ((mx - m_ref) * p.scale_log2 > kRescaleThreshold) {
-        factor = ex2((m_ref - mx) * p.scale_log2);
-        m_ref = mx;
-        l_sum *= factor;
-        rescale = true;
-      }
-      const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
-
-      // P = exp2(S * scale_log2 - ms), packed to 16 bit in place (masked entries are -inf -> 0)
-#pragma unroll
-      for (int i = 0; i < 64; i += 2) {
-        const float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
-        const float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
-        l_sum += a + b;
-        r[i >> 1] = pack2<kFp16>(a, b);
-      }
-
-      // the P buffer and the O accumulators are free once PV(j-1) has completed
-      if (j > 0) {
-        t0 = prof ? clock64() : 0;
-        ok = mbar_wait(ctrl + kBarPvDone, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-        if (prof) t_c += clock64() - t0;
+      for (int j = 0; j < n_steps && ok; ++j, ++gs) {
+        long long t0 = prof ? clock64() : 0;
+        ok = mbar_wait(ctrl + kBarSFull + 8 * (gs & 1), (gs >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        if (prof) t_a += clock64() - t0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-      }
-      if (__any_sync(0xffffffffu, rescale)) {
-        // this warp group rescales its half of the lane's 256 O columns
-#pragma unroll 1
-        for (int c4 = 0; c4 < 4; ++c4) {
-          uint32_t t[32];
-          const uint32_t a = lane_addr + kTmemColsO + wg * 128 + c4 * 32;
-          tmem_ld32(a, t);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
-          tmem_st32(a, t);
-        }
-        tmem_st_wait();
-      }
-      // P row segment -> shared memory, K-major 128B-swizzled [64 rows][64 keys] blocks
-      {
-        const uint32_t blk = sP + (half * 2 + wg) * 8192 + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          st_shared_v4(blk + ((c ^ (row & 7)) << 4), r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(leader_p_full);
-    }
+        const uint32_t s_addr = lane_addr + kTmemColsS + (gs & 1) * 128 + wg * 64;
+        const int key0 = (step0 + j) * kStepKeys + half * 128 + wg * 64;  // key of this thread's column 0
+        const int cl = limit - key0;                                       // columns > cl are masked
+        const int cl_lo = lo_limit - key0;                                 // columns < cl_lo are masked
 
-    if (prof && warp == 4 && lane == 0) {
-      p.debug[100008] = static_cast<float>(t_a);
-      p.debug[100009] = static_cast<float>(t_b);
-      p.debug[100010] = static_cast<float>(t_c);
-      p.debug[100011] = static_cast<float>(clock64() - t_all);
-    }
-    // ---- epilogue
-    if (ok && n_steps > 0) {
-      ok = mbar_wait(ctrl + kBarPvDone, (n_steps - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-      ok = __all_sync(0xffffffffu, ok);
-      tc_fence_after_sync();
-    }
-    float* xs = xchg + (n_steps & 1) * 256;
-    if (ok) {
-      xs[xi] = l_sum;
-      mbar_arrive(xbar);
-      ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      const float l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
+        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        if (p.softcap_pre != 0.f) {
+          // softcap: s <- tanh(s * scale / softcap); scale_log2 then holds softcap * log2(e)
+#pragma unroll
+          for (int i = 0; i < 64; ++i) r[i] = __float_as_uint(tanh_approx(__uint_as_float(r[i]) * p.softcap_pre));
+        }
+        if (cl < 63) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i > cl) r[i] = 0xff800000u;  // -inf
+        }
+        if (cl_lo > 0) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i < cl_lo) r[i] = 0xff800000u;
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+
+        // combine with the three other threads that hold parts of this row
+        float* xs = xchg + (gs & 1) * 256;
+        xs[xi] = mx;
+        t0 = prof ? clock64() : 0;
+        mbar_arrive(xbar);
+        ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+        if (prof) t_b += clock64() - t0;
+        ok = __all_sync(0xffffffffu, ok);
+        xphase ^= 1u;
+        if (!ok) break;
+        mx = fmaxf(fmaxf(mx, xs[xi ^ 64]), fmaxf(xs[xi ^ 128], xs[xi ^ 192]));
+
+        float factor = 1.f;
+        bool rescale = false;
+        if (m_ref == -INFINITY) {
+          m_ref = mx;
+        } else if ((mx - m_ref) * p.scale_log2 > kRescaleThreshold) {
+          factor = ex2((m_ref - mx) * p.scale_log2);
+          m_ref = mx;
+          l_sum *= factor;
+          rescale = true;
+        }
+        const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+
+        // P = exp2(S * scale_log2 - ms), packed to 16 bit in place (masked entries are -inf -> 0)
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
+          const float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
+          l_sum += a + b;
+          r[i >> 1] = pack2<kFp16>(a, b);
+        }
+
+        // the P buffer and the O accumulators are free once PV of the previous step has completed
+        // (for the first step of a tile the epilogue of the previous tile already waited for it)
+        if (j > 0) {
+          t0 = prof ? clock64() : 0;
+          ok = mbar_wait(ctrl + kBarPvDone, (gs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+          if (prof) t_c += clock64() - t0;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+          // this warp group rescales its half of the lane's 256 O columns
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t t[32];
+            const uint32_t a = lane_addr + kTmemColsO + wg * 128 + c4 * 32;
+            tmem_ld32(a, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * factor);
+            tmem_st32(a, t);
+          }
+          tmem_st_wait();
+        }
+        // P row segment -> shared memory, K-major 128B-swizzled [64 rows][64 keys] blocks
+        {
+          const uint32_t blk = sP + (half * 2 + wg) * 8192 + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(blk + ((c ^ (row & 7)) << 4), r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_p_full);
+      }
+      if (!ok) break;
+
+      // ---- epilogue of this tile
+      float l_tot = 0.f;
+      if (n_steps > 0) {
+        ok = mbar_wait(ctrl + kBarPvDone, (gs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // row sums of the four threads of a row; the slot of the tile's last step is safe to reuse here
+        float* xs = xchg + ((gs - 1) & 1) * 256;
+        xs[xi] = l_sum;
+        mbar_arrive(xbar);
+        ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+        ok = __all_sync(0xffffffffu, ok);
+        xphase ^= 1u;
+        if (!ok) break;
+        l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
+      }
       const bool any = l_tot > 0.f;
       const float inv = any ? 1.f / l_tot : 0.f;
-      const bool row_ok = pos < tc.sq;
-      if (row_ok && half == 0 && wg == 0 && p.lse != nullptr) {
+      if (pos < tc.sq && half == 0 && wg == 0 && p.lse != nullptr) {
         const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
         const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + tc.q_off + pos
                                    : (static_cast<int64_t>(tc.b) * g.heads_q + head) * tc.sq + pos;
         p.lse[idx] = lse;
       }
-      // Epilogue stores: each thread owns one row, so a plain 16-byte store per thread would touch 32
-      // different lines per warp instruction. 8 x 8 chunk transposes inside groups of 8 lanes make every
-      // store instruction write 4 full 128-byte lines instead.
+      // Stores: each thread owns one row, so a plain 16-byte store per thread would touch 32 different
+      // lines per warp instruction. 8 x 8 chunk transposes inside groups of 8 lanes make every store
+      // instruction write 4 full 128-byte lines instead.
       uint16_t* obase = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b);
-      const int grp_row0 = row & ~7;  // first row of this lane's group of 8
 #pragma unroll 1
       for (int c2 = 0; c2 < 2; ++c2) {
         uint32_t t[64];
@@ -422,11 +506,11 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
           tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
           tmem_ld_wait();
-        }
-        if (dump) {
-          float* dst = p.debug + 32768 + (static_cast<int>(rank) * 128 + L) * 256 + wg * 128 + c2 * 64;
-#pragma unroll
-          for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(t[i]);
+          if (c2 == 1) {  // O has been read: the next tile's first PV may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_o_free);
+          }
         }
         uint32_t x[32];
 #pragma unroll
@@ -436,24 +520,25 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           x[i >> 1] = pack2<kFp16>(a, b);
         }
         transpose_chunks_8x8(x, lane);
-        // now x[4r..4r+3] = 16-byte chunk (lane & 7) of row grp_row0 + r
+        // now x[4e..4e+3] = 16-byte chunk (lane & 7) of row grp_row0 + e
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          const int rr = grp_row0 + r;
-          const int pos_r = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + rr / g.pack_g;
-          const int head_r = (g.pack_g > 1) ? tc.hu * g.pack_g + rr % g.pack_g : tc.hu;
-          if (pos_r < tc.sq) {
-            uint16_t* dst = obase + static_cast<int64_t>(tc.q_off + pos_r) * p.o_stride_s +
-                            static_cast<int64_t>(head_r) * p.o_stride_h + wg * 256 + half * 128 + c2 * 64 + (lane & 7) * 8;
-            st_global_v4(dst, x[4 * r], x[4 * r + 1], x[4 * r + 2], x[4 * r + 3]);
+        for (int e = 0; e < 8; ++e) {
+          const int re = grp_row0 + e;
+          const int pos_e = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + re / g.pack_g;
+          const int head_e = (g.pack_g > 1) ? tc.hu * g.pack_g + re % g.pack_g : tc.hu;
+          if (pos_e < tc.sq) {
+            uint16_t* dst = obase + static_cast<int64_t>(tc.q_off + pos_e) * p.o_stride_s +
+                            static_cast<int64_t>(head_e) * p.o_stride_h + wg * 256 + half * 128 + c2 * 64 + (lane & 7) * 8;
+            st_global_v4(dst, x[4 * e], x[4 * e + 1], x[4 * e + 2], x[4 * e + 3]);
           }
         }
       }
-      if (dump && wg == 0) {
-        float* dst = p.debug + 32768 + 65536 + (static_cast<int>(rank) * 128 + L) * 2;
-        dst[0] = m_ref;
-        dst[1] = l_tot;
-      }
+    }
+    if (prof && warp == 4 && lane == 0) {
+      p.debug[100008] = static_cast<float>(t_a);
+      p.debug[100009] = static_cast<float>(t_b);
+      p.debug[100010] = static_cast<float>(t_c);
+      p.debug[100011] = static_cast<float>(clock64() - t_all);
     }
   }
 
@@ -491,6 +576,13 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   fp.o_stride_h = p->o_strides[2];
   fp.total_q = p->total_q;
   fp.scale_log2 = p->softmax_scale * kLog2e;
+  fp.softcap_pre = 0.f;
+  if (p->softcap > 0.f) {
+    fp.softcap_pre = p->softmax_scale / p->softcap;
+    fp.scale_log2 = p->softcap * kLog2e;
+  }
+  fp.win_left = p->window_left;
+  fp.win_right = p->causal ? 0 : p->window_right;
   fp.status = p->status_flag;
   fp.debug = p->debug;
 
@@ -498,10 +590,40 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   const long long pairs = varlen ? static_cast<long long>(g.row_tiles) * g.head_units
                                  : static_cast<long long>(g.row_tiles) * g.head_units * g.batch;
   if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "forward grid out of range");
+  fp.total_pairs = static_cast<int>(pairs);
   auto kern = p->dtype == SPLITD_DTYPE_FP16 ? splitd_fwd_kernel<true> : splitd_fwd_kernel<false>;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::kSmemBytes);
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(ce));
-  kern<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(384), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
+  // persistent grid: as many CTA pairs as the device can keep resident at once
+  int dev = 0, resident = 0;
+  cudaGetDevice(&dev);
+  static int cached_pairs[64][2] = {};
+  const int dt = p->dtype == SPLITD_DTYPE_FP16 ? 1 : 0;
+  if (dev >= 0 && dev < 64 && cached_pairs[dev][dt] > 0) {
+    resident = cached_pairs[dev][dt];
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2);
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = fwd::kSmemBytes;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    ce = cudaOccupancyMaxActiveClusters(&resident, kern, &cfg);
+    if (ce != cudaSuccess || resident <= 0) {
+      cudaGetLastError();
+      int sms = 0;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      resident = sms > 1 ? sms / 2 : 1;
+    }
+    if (dev >= 0 && dev < 64) cached_pairs[dev][dt] = resident;
+  }
+  const long long launch_pairs = pairs < resident ? pairs : resident;
+  kern<<<dim3(static_cast<unsigned>(2 * launch_pairs)), dim3(384), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(ce));
   return 0;

@@ -351,6 +351,11 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 template <bool kFp16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (kFp16) {

@@ -78,6 +78,9 @@ class SplitdParams(ctypes.Structure):
         ("dtype", ctypes.c_int32),
         ("status_flag", ctypes.c_void_p),
         ("debug", ctypes.c_void_p),
+        ("softcap", ctypes.c_float),
+        ("window_left", ctypes.c_int32),
+        ("window_right", ctypes.c_int32),
     ]
 
 

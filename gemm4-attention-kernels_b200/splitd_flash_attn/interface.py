@@ -188,7 +188,10 @@ def _resolve_causal_local_window(causal, window_size_left, window_size_right):
 
 
 def _unsupported_features(requires_grad, softcap, local, score_mod=None, aux_tensors=None) -> None:
-    """Sliding-window and softcap are not built for sm_100a in either direction."""
+    """softcap and sliding windows are forward-only, as in the reference
+    (``_unsupported_training_features``, interface.py:264-286)."""
+    if not requires_grad:
+        return
     unsupported = []
     if softcap is not None and softcap != 0.0:
         unsupported.append("softcap")
@@ -199,8 +202,7 @@ def _unsupported_features(requires_grad, softcap, local, score_mod=None, aux_ten
     if aux_tensors is not None:
         unsupported.append("aux_tensors")
     if unsupported:
-        what = "backward" if requires_grad else "B200 build"
-        raise NotImplementedError(f"SplitD {what} does not support " + ", ".join(unsupported) + ".")
+        raise NotImplementedError("SplitD backward does not support training with " + ", ".join(unsupported) + ".")
 
 
 # ---------------------------------------------------------------------------
@@ -271,6 +273,8 @@ def _fill_params(q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale, causal, deb
     p.dtype = _capi.SPLITD_DTYPE_FP16 if q.dtype == torch.float16 else _capi.SPLITD_DTYPE_BF16
     p.status_flag = _ptr(_status_flag(q.device))
     p.debug = _ptr(debug)
+    p.softcap = 0.0
+    p.window_left = p.window_right = -1
     return p
 
 
@@ -347,6 +351,11 @@ def _flash_attn_fwd(
     params = _fill_params(
         q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, debug
     )
+    if softcap is not None:
+        params.softcap = float(softcap)
+    if local:  # negative or missing side = unbounded on that side
+        params.window_left = -1 if window_size_left is None or window_size_left < 0 else int(window_size_left)
+        params.window_right = -1 if window_size_right is None or window_size_right < 0 else int(window_size_right)
     with torch.cuda.device(device):
         _capi.check(_capi.load_library().splitd_fwd(ctypes.byref(params), _stream_ptr(device)))
     return out, lse
@@ -498,57 +507,152 @@ class FlashAttnFunc(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None
 
 
-class FlashAttnVarlenFunc(torch.autograd.Function):
-    @staticmethod
-    def forward(
-        ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, window_size, softcap
-    ):
-        out, lse = _flash_attn_fwd(
-            q,
-            k,
-            v,
-            cu_seqlens_q=cu_seqlens_q,
-            cu_seqlens_k=cu_seqlens_k,
-            max_seqlen_q=max_seqlen_q,
-            max_seqlen_k=max_seqlen_k,
-            softmax_scale=softmax_scale,
-            causal=causal,
-            window_size_left=window_size[0],
-            window_size_right=window_size[1],
-            softcap=softcap,
-            return_lse=True,
-        )
-        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k)
-        ctx.max_seqlen_q, ctx.max_seqlen_k = max_seqlen_q, max_seqlen_k
-        ctx.softmax_scale, ctx.causal = softmax_scale, causal
-        ctx.window_size, ctx.softcap = window_size, softcap
-        ctx.set_materialize_grads(False)
-        return out, lse
+# ---------------------------------------------------------------------------
+# PyTorch custom ops for the packed layout (same op names, schemas and fake kernels as the reference's
+# ``splitd_flash_attn::varlen_fwd`` / ``varlen_bwd``, interface.py:909-1109), so the packed path can be
+# traced by FakeTensor / torch.compile. Optional window ints are encoded as -2**31 for "None".
+# ---------------------------------------------------------------------------
+_NONE_INT = -(2**31)
 
-    @staticmethod
-    def backward(ctx, dout, dlse):
-        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
-        if dout is None:
-            dout = torch.zeros_like(out)
-        dq, dk, dv = _flash_attn_bwd(
-            q,
-            k,
-            v,
-            out,
-            dout,
-            lse,
-            ctx.softmax_scale,
-            ctx.causal,
-            ctx.softcap,
-            window_size_left=ctx.window_size[0],
-            window_size_right=ctx.window_size[1],
-            cu_seqlens_q=cu_q,
-            cu_seqlens_k=cu_k,
-            max_seqlen_q=ctx.max_seqlen_q,
-            max_seqlen_k=ctx.max_seqlen_k,
-            dlse=dlse,
-        )
-        return (dq, dk, dv) + (None,) * 8
+
+def _enc(v: Optional[int]) -> int:
+    return _NONE_INT if v is None else int(v)
+
+
+def _dec(v: int) -> Optional[int]:
+    return None if v == _NONE_INT else v
+
+
+@torch.library.custom_op("splitd_flash_attn::varlen_fwd", mutates_args=())
+def _varlen_fwd_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    pack_gqa: bool,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    return _flash_attn_fwd(
+        q,
+        k,
+        v,
+        cu_seqlens_q=cu_seqlens_q,
+        cu_seqlens_k=cu_seqlens_k,
+        max_seqlen_q=max_seqlen_q,
+        max_seqlen_k=max_seqlen_k,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        softcap=softcap,
+        pack_gqa=pack_gqa,
+        return_lse=True,
+    )
+
+
+def _fake_shapes(q, k, v, cu_seqlens_q, cu_seqlens_k):
+    """Shape / dtype checks that need no device values (what a fake kernel may look at)."""
+    if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
+        raise ValueError("q, k and v must be rank-3 packed tensors")
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise TypeError("cu_seqlens must have dtype torch.int32")
+    _validate_head_dims(q.shape[-1], v.shape[-1])
+    if q.shape[-2] % k.shape[-2] != 0:
+        raise ValueError(f"num_head ({q.shape[-2]}) must be divisible by num_head_kv ({k.shape[-2]})")
+
+
+@torch.library.register_fake("splitd_flash_attn::varlen_fwd")
+def _varlen_fwd_fake(
+    q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, window_size_left,
+    window_size_right, softcap, pack_gqa,
+):
+    _fake_shapes(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    _validate_training_dtype(q, q.requires_grad or k.requires_grad or v.requires_grad)
+    out = q.new_empty((q.shape[0], q.shape[1], v.shape[-1]))
+    lse = q.new_empty((q.shape[1], q.shape[0]), dtype=torch.float32)
+    return out, lse
+
+
+@torch.library.custom_op("splitd_flash_attn::varlen_bwd", mutates_args=())
+def _varlen_bwd_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    dout: torch.Tensor,
+    lse: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    dlse: Optional[torch.Tensor],
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _flash_attn_bwd(
+        q,
+        k,
+        v,
+        out,
+        dout,
+        lse,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        softcap=softcap,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        cu_seqlens_q=cu_seqlens_q,
+        cu_seqlens_k=cu_seqlens_k,
+        max_seqlen_q=max_seqlen_q,
+        max_seqlen_k=max_seqlen_k,
+        dlse=dlse,
+    )
+
+
+@torch.library.register_fake("splitd_flash_attn::varlen_bwd")
+def _varlen_bwd_fake(
+    q, k, v, out, dout, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
+    window_size_left, window_size_right, softcap, dlse,
+):
+    _fake_shapes(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    if q.dtype == torch.float16:
+        raise NotImplementedError("SplitD backward currently supports bfloat16 only.")
+    if softcap != 0.0:
+        raise NotImplementedError("SplitD backward does not support softcap yet")
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _varlen_setup_context(ctx, inputs, output) -> None:
+    q, k, v, cu_seqlens_q, cu_seqlens_k = inputs[:5]
+    ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal = inputs[5:9]
+    ctx.window_size_left, ctx.window_size_right, ctx.softcap = inputs[9:12]
+    out, lse = output
+    ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k)
+    ctx.set_materialize_grads(False)
+
+
+def _varlen_backward(ctx, dout, dlse):
+    q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+    if dout is None:
+        dout = torch.zeros_like(out)
+    dq, dk, dv = torch.ops.splitd_flash_attn.varlen_bwd(
+        q, k, v, out, dout, lse, cu_q, cu_k, ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal,
+        ctx.window_size_left, ctx.window_size_right, ctx.softcap, dlse,
+    )
+    return dq, dk, dv, *((None,) * 10)
+
+
+torch.library.register_autograd("splitd_flash_attn::varlen_fwd", _varlen_backward, setup_context=_varlen_setup_context)
 
 
 # ---------------------------------------------------------------------------
@@ -612,7 +716,9 @@ def split_flash_attn_varlen_func(
         raise TypeError("window_size must be a tuple of (left, right)")
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
-    out, lse = FlashAttnVarlenFunc.apply(
+    if pack_gqa is None:
+        pack_gqa = q.shape[-2] > k.shape[-2]
+    out, lse = torch.ops.splitd_flash_attn.varlen_fwd(
         q,
         k,
         v,
@@ -621,8 +727,10 @@ def split_flash_attn_varlen_func(
         max_seqlen_q,
         max_seqlen_k,
         float(softmax_scale),
-        causal,
-        window_size,
-        softcap,
+        bool(causal),
+        _enc(window_size[0]),
+        _enc(window_size[1]),
+        float(softcap),
+        bool(pack_gqa),
     )
     return (out, lse) if return_lse else out

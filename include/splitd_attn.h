@@ -82,8 +82,15 @@ typedef struct {
   /* device word; a kernel that gives up a bounded wait stores a positive code here (0 = fine). */
   int32_t* status_flag; /* may be NULL */
 
-  /* optional fp32 device buffer receiving raw accumulator dumps of the first tile (tests only) */
+  /* optional fp32 device buffer receiving per-role cycle counters of one CTA pair (tests / tuning only) */
   float* debug;
+
+  /* ---- forward-only score modifiers (the backward rejects them, like src/interface.py:676-683) ---- */
+  float softcap;        /* > 0: scores become softcap * tanh(scale * qk / softcap) before masking; 0 = off
+                           (src/interface.py:446-449, src/utils.py:104-110)                              */
+  int32_t window_left;  /* >= 0: keys j < i + Sk - Sq - window_left are hidden; -1 = unbounded           */
+  int32_t window_right; /* >= 0: keys j > i + Sk - Sq + window_right are hidden; -1 = unbounded          */
+                        /* (sliding window of src/block_info.py:44-59; `causal` is window_right = 0)      */
 } splitd_params;
 
 /* 1 if `device` can run this library (compute capability 10.x), 0 if not, <0 on CUDA error.

@@ -44,6 +44,20 @@ def _causal_mask(rows: torch.Tensor, sk: int, sq: int, device) -> torch.Tensor:
     return cols[None, :] > (rows[:, None] + (sk - sq))
 
 
+def _window_mask(rows: torch.Tensor, sk: int, sq: int, window, device) -> torch.Tensor:
+    """Sliding window (left, right), None / negative = unbounded: key j is hidden from query i when
+    j > i + sk - sq + right or j < i + sk - sq - left (src/testing.py:237-266 of the reference)."""
+    cols = torch.arange(sk, device=device)[None, :]
+    diag = rows[:, None] + (sk - sq)
+    m = torch.zeros(rows.numel(), sk, dtype=torch.bool, device=device)
+    left, right = window
+    if right is not None and right >= 0:
+        m |= cols > diag + right
+    if left is not None and left >= 0:
+        m |= cols < diag - left
+    return m
+
+
 def attention_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -51,8 +65,12 @@ def attention_fwd(
     causal: bool = False,
     softmax_scale: Optional[float] = None,
     compute_dtype: torch.dtype = torch.float32,
+    softcap: float = 0.0,
+    window: Tuple[Optional[int], Optional[int]] = (None, None),
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """q (B,Sq,Hq,D), k/v (B,Sk,Hkv,D) -> out (B,Sq,Hq,D) fp32, lse (B,Hq,Sq) fp32."""
+    """q (B,Sq,Hq,D), k/v (B,Sk,Hkv,D) -> out (B,Sq,Hq,D) fp32, lse (B,Hq,Sq) fp32.
+    softcap > 0: scores = softcap * tanh(scores / softcap) before masking
+    (tests/test_flash_fwd_splitd_sdpa.py:111-113); window: see _window_mask."""
     B, sq, hq, d = q.shape
     sk, hkv = k.shape[1], k.shape[2]
     g = hq // hkv
@@ -68,9 +86,13 @@ def attention_fwd(
                 r1 = min(sq, r0 + ROW_BLOCK)
                 qh = q[b, r0:r1, h * g : (h + 1) * g].to(compute_dtype)  # (R, G, D)
                 s = torch.einsum("rgd,kd->grk", qh * scale, kh)  # (G, R, Sk)
+                if softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
+                rows = torch.arange(r0, r1, device=dev)
                 if causal:
-                    m = _causal_mask(torch.arange(r0, r1, device=dev), sk, sq, dev)
-                    s = s.masked_fill(m[None], float("-inf"))
+                    s = s.masked_fill(_causal_mask(rows, sk, sq, dev)[None], float("-inf"))
+                if window[0] is not None or window[1] is not None:
+                    s = s.masked_fill(_window_mask(rows, sk, sq, window, dev)[None], float("-inf"))
                 l = torch.logsumexp(s, dim=-1)  # (G, R)
                 p = torch.exp(s - torch.where(torch.isinf(l), torch.zeros_like(l), l)[..., None])
                 p = torch.where(torch.isinf(l)[..., None], torch.zeros_like(p), p)
@@ -127,7 +149,8 @@ def attention_bwd(
 
 
 def attention_math_lowp(
-    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False, softmax_scale: Optional[float] = None
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False, softmax_scale: Optional[float] = None,
+    softcap: float = 0.0, window: Tuple[Optional[int], Optional[int]] = (None, None),
 ) -> torch.Tensor:
     """Error yardstick: matmuls in the input's 16-bit dtype, softmax in fp32, probabilities cast back
     (tests/test_flash_fwd_splitd_sdpa.py:160-185). Returns (B,Sq,Hq,D) in the input dtype."""
@@ -139,9 +162,13 @@ def attention_math_lowp(
     kt = k.transpose(1, 2).repeat_interleave(g, dim=1)
     vt = v.transpose(1, 2).repeat_interleave(g, dim=1)
     s = torch.matmul(qt * scale, kt.transpose(-2, -1))
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    rows = torch.arange(sq, device=q.device)
     if causal:
-        m = _causal_mask(torch.arange(sq, device=q.device), sk, sq, q.device)
-        s = s.masked_fill(m, float("-inf"))
+        s = s.masked_fill(_causal_mask(rows, sk, sq, q.device), float("-inf"))
+    if window[0] is not None or window[1] is not None:
+        s = s.masked_fill(_window_mask(rows, sk, sq, window, q.device), float("-inf"))
     attn = torch.softmax(s, dim=-1, dtype=torch.float32)
     attn = torch.nan_to_num(attn, nan=0.0).to(q.dtype)
     return torch.matmul(attn, vt).transpose(1, 2)

@@ -55,3 +55,26 @@ def test_library_is_mandatory(monkeypatch):
     monkeypatch.setattr(_capi, "LIB_PATH", "/nonexistent/libsplitd_attn.so")
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _capi.load_library()
+
+
+def test_varlen_custom_op_traces_under_fake_tensors():
+    """The packed path is a torch.library custom op pair with fake kernels (like the reference's
+    splitd_flash_attn::varlen_fwd / varlen_bwd, interface.py:909-1061): shapes propagate without a GPU."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from splitd_flash_attn import split_flash_attn_varlen_func
+
+    with FakeTensorMode():
+        q = torch.empty(96, 8, D, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        kv = torch.empty(96, 2, D, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        cu = torch.empty(4, dtype=torch.int32, device="cuda")
+        out, lse = split_flash_attn_varlen_func(q, kv, kv, cu, cu, 40, 40, causal=True, return_lse=True)
+        assert out.shape == (96, 8, D) and out.dtype == torch.bfloat16
+        assert lse.shape == (8, 96) and lse.dtype == torch.float32
+        # the fake backward kernel (the autograd engine itself needs a real CUDA device, so call the op)
+        gq, gk, gv = torch.ops.splitd_flash_attn.varlen_bwd(
+            q.detach(), kv.detach(), kv.detach(), out.detach(), out.detach(), lse, cu, cu, 40, 40, 0.05, True,
+            -(2**31), -(2**31), 0.0, None,
+        )
+        assert gq.shape == q.shape and gk.shape == kv.shape and gv.shape == kv.shape
+    assert hasattr(torch.ops.splitd_flash_attn, "varlen_fwd") and hasattr(torch.ops.splitd_flash_attn, "varlen_bwd")

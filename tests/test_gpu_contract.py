@@ -83,16 +83,12 @@ def test_too_small_max_seqlen():
         split_flash_attn_varlen_func(_t(64, 2, D), _t(64, 2, D), _t(64, 2, D), cu, cu, 20, 64)
 
 
-def test_unsupported_features_raise():
+def test_window_resolution_on_device():
     from splitd_flash_attn import split_flash_attn_func
 
     q, k, v = _t(1, 64, 2, D), _t(1, 64, 2, D), _t(1, 64, 2, D)
     with pytest.raises(ValueError, match="mutually exclusive"):
         split_flash_attn_func(q, k, v, causal=True, window_size=(16, 0))
-    with pytest.raises(NotImplementedError):
-        split_flash_attn_func(q, k, v, softcap=15.0)
-    with pytest.raises(NotImplementedError):
-        split_flash_attn_func(q, k, v, window_size=(16, 16))
     # (-1, 0) is the causal window, (-1, -1) the full one (interface.py:297-318 of the reference)
     a = split_flash_attn_func(q, k, v, window_size=(-1, 0))
     b = split_flash_attn_func(q, k, v, causal=True)
