@@ -83,12 +83,12 @@ int check_common(const splitd_params* p, bool backward) {
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "seqlen_q and seqlen_k must be > 0");
   }
   if (p->softcap < 0.f) return fail(SPLITD_ERR_INVALID_ARGUMENT, "softcap must be >= 0");
-  if (p->window_left < -1 || p->window_right < -1)
+  if (p->local && (p->window_left < -1 || p->window_right < -1))
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "window_left / window_right must be >= -1");
-  if (p->causal && (p->window_left >= 0 || p->window_right >= 0))
+  if (p->causal && p->local)
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "causal and a sliding window are mutually exclusive");
   if (backward) {
-    if (p->softcap > 0.f || p->window_left >= 0 || p->window_right >= 0)
+    if (p->softcap > 0.f || p->local)
       return fail(SPLITD_ERR_UNSUPPORTED, "backward does not support softcap or sliding windows");
     if (p->dtype != SPLITD_DTYPE_BF16)
       return fail(SPLITD_ERR_UNSUPPORTED, "backward supports bfloat16 only");

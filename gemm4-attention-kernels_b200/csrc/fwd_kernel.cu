@@ -581,8 +581,8 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
     fp.softcap_pre = p->softmax_scale / p->softcap;
     fp.scale_log2 = p->softcap * kLog2e;
   }
-  fp.win_left = p->window_left;
-  fp.win_right = p->causal ? 0 : p->window_right;
+  fp.win_left = p->local ? p->window_left : -1;
+  fp.win_right = p->causal ? 0 : (p->local ? p->window_right : -1);
   fp.status = p->status_flag;
   fp.debug = p->debug;
 

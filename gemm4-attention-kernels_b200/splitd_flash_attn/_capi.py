@@ -79,6 +79,7 @@ class SplitdParams(ctypes.Structure):
         ("status_flag", ctypes.c_void_p),
         ("debug", ctypes.c_void_p),
         ("softcap", ctypes.c_float),
+        ("local", ctypes.c_int32),
         ("window_left", ctypes.c_int32),
         ("window_right", ctypes.c_int32),
     ]

@@ -274,7 +274,7 @@ def _fill_params(q, k, v, out, lse, cu_q, cu_k, max_q, max_k, scale, causal, deb
     p.status_flag = _ptr(_status_flag(q.device))
     p.debug = _ptr(debug)
     p.softcap = 0.0
-    p.window_left = p.window_right = -1
+    p.local = 0
     return p
 
 
@@ -354,6 +354,7 @@ def _flash_attn_fwd(
     if softcap is not None:
         params.softcap = float(softcap)
     if local:  # negative or missing side = unbounded on that side
+        params.local = 1
         params.window_left = -1 if window_size_left is None or window_size_left < 0 else int(window_size_left)
         params.window_right = -1 if window_size_right is None or window_size_right < 0 else int(window_size_right)
     with torch.cuda.device(device):

@@ -88,6 +88,7 @@ typedef struct {
   /* ---- forward-only score modifiers (the backward rejects them, like src/interface.py:676-683) ---- */
   float softcap;        /* > 0: scores become softcap * tanh(scale * qk / softcap) before masking; 0 = off
                            (src/interface.py:446-449, src/utils.py:104-110)                              */
+  int32_t local;        /* 0: no sliding window, the two fields below are ignored (so zeroed params are safe) */
   int32_t window_left;  /* >= 0: keys j < i + Sk - Sq - window_left are hidden; -1 = unbounded           */
   int32_t window_right; /* >= 0: keys j > i + Sk - Sq + window_right are hidden; -1 = unbounded          */
                         /* (sliding window of src/block_info.py:44-59; `causal` is window_right = 0)      */

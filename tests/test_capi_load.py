@@ -50,7 +50,6 @@ def test_invalid_arguments_are_rejected_without_a_gpu():
     lib = _capi.load_library()
     assert lib.splitd_fwd(None, None) == -1
     p = _capi.SplitdParams()
-    p.window_left = p.window_right = -1
     assert lib.splitd_fwd(ctypes.byref(p), None) == -1  # NULL tensors
     assert b"NULL" in lib.splitd_last_error()
     p.q = p.k = p.v = p.o = 1 << 20
