@@ -396,4 +396,30 @@ __device__ __forceinline__ void transpose_chunks_8x8(uint32_t (&x)[32], int lane
   }
 }
 
+// Same idea with 32-byte chunks: x[8*c .. 8*c+7] = chunk c (of 4) of ONE row per thread; afterwards
+// x[8*r .. 8*r+7] in lane l is chunk (l & 3) of row (lane & ~3) + r. With 256-bit stores a warp then writes
+// 8 full 128-byte lines per instruction.
+__device__ __forceinline__ void transpose_chunks32_4x4(uint32_t (&x)[32], int lane) {
+#pragma unroll
+  for (int m = 1; m < 4; m <<= 1) {
+    const bool up = (lane & m) != 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (c & m) continue;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const uint32_t a = x[8 * c + w], b = x[8 * (c | m) + w];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, up ? a : b, m);
+        x[8 * c + w] = up ? recv : a;
+        x[8 * (c | m) + w] = up ? b : recv;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 }  // namespace sd
