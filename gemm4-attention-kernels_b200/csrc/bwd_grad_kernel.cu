@@ -18,36 +18,139 @@
 // of the 512 output columns; the pair shares B through the 2-SM MMA).
 // Operand forms: P^T / dS^T are read straight from the [rows][keys] workspace as MN-major A; dS for dQ
 // is the same memory read as K-major A; dO, Q and K rows are MN-major B.
+//
+// Persistent pairs: the grid is one pair per SM pair, each drawing output tiles (dV/dK tiles first, then
+// dQ tiles, heaviest first) from a global counter (tile_queue.cuh). The producer keeps streaming the next tile's operands while the epilogue
+// warps drain the accumulator, and nothing is re-initialised between tiles.
 #include <cstring>
 
 #include "common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
+#include "tile_queue.cuh"
 
 namespace sd {
 
 namespace grad {
-constexpr int kRowsPerPairOut = 256;
 constexpr int kStages = 4;
 constexpr int kStageBytes = 49152;  // A: 2 x 8 KB, B: 4 x 8 KB
 constexpr int kOffCtrl = kStages * kStageBytes;
 constexpr int kBarFull = 0;
 constexpr int kBarEmpty = 8 * kStages;
 constexpr int kBarAccDone = kBarEmpty + 8 * kStages;
-constexpr int kTmemPtr = kBarAccDone + 8;
+constexpr int kBarAccFree = kBarAccDone + 8;
+constexpr int kTmemPtr = kBarAccFree + 8;
 constexpr int kAbort = kTmemPtr + 4;
+constexpr int kTileQ = kAbort + 4;  // TileQueue, kTileQueueBytes
+constexpr int kConsumers = 2 + 1 + 16;  // producers, MMA issuer, epilogue warps of both CTAs
 constexpr int kCtrlBytes = 256;
 constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
+constexpr int kThreads = 384;  // producer, MMA issuer, 2 idle warps, 8 epilogue warps
 enum { kModeDV = 0, kModeDK = 1, kModeDQ = 2 };
 }  // namespace grad
 
 struct GradLaunch {
-  int n_kv_pairs;   // pairs producing dV / dK (even: dV, odd: dK)
-  int n_dq_pairs;   // pairs producing dQ
-  int dq_pairs_per_unit;  // packed layout: upper bound of dQ pairs per head unit; batched: per sequence
+  int n_kv_pairs;         // tiles producing dV / dK (even: dV, odd: dK)
+  int n_dq_pairs;         // tiles producing dQ
+  int dq_pairs_per_unit;  // packed layout: upper bound of dQ tiles per head unit; batched: per sequence
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+// One output tile of a CTA pair.
+struct GradTile {
+  int mode, b, sq, sk, q_off, k_off, tile_base, n_row_tiles;
+  int kvh, kt;      // dK/dV: kv head, key tile (256 keys)
+  int hu, tp;       // dQ: head unit, tile pair
+  int n_stages, t_min, units;
+};
+
+// Decode tile `idx` of the launch. Returns false when the slot holds no tile.
+__device__ __forceinline__ bool grad_decode(const BwdParams& p, const GradLaunch& gl, int idx, GradTile& t) {
+  const TileGeom& g = p.g;
+  const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
+  const bool folded = g.pack_g == g.group;
+  t.q_off = 0, t.k_off = 0, t.t_min = 0, t.units = 1, t.kvh = 0, t.kt = 0, t.hu = 0, t.tp = 0, t.n_stages = 0;
+  if (idx < gl.n_kv_pairs) {
+    t.mode = idx & 1;
+    int i2 = idx >> 1;
+    if (g.cu_q == nullptr) {
+      t.kt = i2 % p.key_tiles;  // heaviest key tile of a sequence first under a causal mask
+      i2 /= p.key_tiles;
+      t.b = i2 % g.batch;
+      t.kvh = i2 / g.batch;
+      t.sq = g.seqlen_q, t.sk = g.seqlen_k;
+      t.n_row_tiles = g.row_tiles;
+      t.tile_base = t.b * g.row_tiles;
+    } else {
+      t.kvh = i2 / p.key_tiles;
+      const int r = i2 - t.kvh * p.key_tiles;
+      int acc_k = 0, acc_r = 0;
+      t.b = -1;
+      for (int i = 0; i < g.batch; ++i) {
+        const int k0 = g.cu_k[i], k1 = g.cu_k[i + 1], q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
+        const int nkt = (k1 - k0 + 255) / 256, nrt = (q1 - q0 + ppp - 1) / ppp;
+        if (r < acc_k + nkt) {
+          t.b = i, t.kt = r - acc_k, t.sq = q1 - q0, t.sk = k1 - k0, t.q_off = q0, t.k_off = k0, t.n_row_tiles = nrt;
+          break;
+        }
+        acc_k += nkt;
+        acc_r += nrt;
+      }
+      if (t.b < 0) return false;
+      t.tile_base = acc_r;
+    }
+    if (t.kvh >= g.heads_kv) return false;
+    if (g.causal) {  // first row tile that can see this key tile (bottom-right aligned)
+      const int x = t.kt * 256 - (t.sk - t.sq);
+      t.t_min = x > 0 ? x / ppp : 0;
+    }
+    t.units = folded ? 1 : g.group;
+    t.n_stages = t.units * max(t.n_row_tiles - t.t_min, 0) * 2;  // 64-row chunks
+  } else {
+    t.mode = grad::kModeDQ;
+    int i2 = idx - gl.n_kv_pairs;
+    if (i2 >= gl.n_dq_pairs) return false;
+    if (g.cu_q == nullptr) {
+      t.tp = i2 % gl.dq_pairs_per_unit;
+      i2 /= gl.dq_pairs_per_unit;
+      t.b = i2 % g.batch;
+      t.hu = i2 / g.batch;
+      if (g.causal) t.tp = gl.dq_pairs_per_unit - 1 - t.tp;  // heaviest first
+      t.sq = g.seqlen_q, t.sk = g.seqlen_k;
+      t.n_row_tiles = g.row_tiles;
+      t.tile_base = t.b * g.row_tiles;
+    } else {
+      t.hu = i2 / gl.dq_pairs_per_unit;
+      const int r = i2 - t.hu * gl.dq_pairs_per_unit;
+      int acc_p = 0, acc_r = 0;
+      t.b = -1;
+      for (int i = 0; i < g.batch; ++i) {
+        const int q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
+        const int nrt = (q1 - q0 + ppp - 1) / ppp, np = (nrt + 1) / 2;
+        if (r < acc_p + np) {
+          t.b = i, t.tp = r - acc_p, t.sq = q1 - q0, t.q_off = q0, t.n_row_tiles = nrt;
+          t.k_off = g.cu_k[i];
+          t.sk = g.cu_k[i + 1] - t.k_off;
+          if (g.causal) t.tp = np - 1 - t.tp;
+          break;
+        }
+        acc_p += np;
+        acc_r += nrt;
+      }
+      if (t.b < 0) return false;
+      t.tile_base = acc_r;
+    }
+    if (t.hu >= g.head_units) return false;
+    t.kvh = folded ? t.hu : t.hu / g.group;
+    // key extent written for this tile pair = that of its last tile, in 256-key blocks
+    const int t_last = min(2 * t.tp + 1, t.n_row_tiles - 1);
+    int kv_hi = t.sk;
+    if (g.causal) kv_hi = min(kv_hi, min((t_last + 1) * ppp, t.sq) + t.sk - t.sq);
+    t.n_stages = kv_hi > 0 ? ((kv_hi + 255) / 256) * 4 : 0;  // 64-key chunks
+  }
+  return true;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(grad::kThreads, 1)
 splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_constant__ CUtensorMap tm_do,
                        const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const BwdParams p, const GradLaunch gl) {
@@ -65,93 +168,12 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());
-  const int pair_id = blockIdx.x >> 1;
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
   const bool folded = g.pack_g == g.group;
-
-  // ------------------------------------------------------------------ what does this pair compute
-  int mode, b = 0, sq = 0, sk = 0, q_off = 0, k_off = 0, tile_base = 0, n_row_tiles = 0;
-  int kvh = 0, kt = 0;            // dK/dV: kv head, key tile (256 keys)
-  int hu = 0, tp = 0;             // dQ: head unit, tile pair
-  int n_stages = 0, t_min = 0, units = 1;
-  if (pair_id < gl.n_kv_pairs) {
-    mode = pair_id & 1;
-    int idx = pair_id >> 1;
-    if (g.cu_q == nullptr) {
-      kt = idx % p.key_tiles;
-      idx /= p.key_tiles;
-      b = idx % g.batch;
-      kvh = idx / g.batch;
-      sq = g.seqlen_q, sk = g.seqlen_k;
-      n_row_tiles = g.row_tiles;
-      tile_base = b * g.row_tiles;
-    } else {
-      kvh = idx / p.key_tiles;
-      const int r = idx - kvh * p.key_tiles;
-      int acc_k = 0, acc_r = 0;
-      b = -1;
-      for (int i = 0; i < g.batch; ++i) {
-        const int k0 = g.cu_k[i], k1 = g.cu_k[i + 1], q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
-        const int nkt = (k1 - k0 + 255) / 256, nrt = (q1 - q0 + ppp - 1) / ppp;
-        if (r < acc_k + nkt) {
-          b = i, kt = r - acc_k, sq = q1 - q0, sk = k1 - k0, q_off = q0, k_off = k0, n_row_tiles = nrt;
-          break;
-        }
-        acc_k += nkt;
-        acc_r += nrt;
-      }
-      if (b < 0) return;
-      tile_base = acc_r;
-    }
-    if (kvh >= g.heads_kv) return;
-    if (g.causal) {  // first row tile that can see this key tile (bottom-right aligned)
-      const int x = kt * 256 - (sk - sq);
-      t_min = x > 0 ? x / ppp : 0;
-    }
-    units = folded ? 1 : g.group;
-    n_stages = units * max(n_row_tiles - t_min, 0) * 2;  // 64-row chunks
-  } else {
-    mode = kModeDQ;
-    int idx = pair_id - gl.n_kv_pairs;
-    if (g.cu_q == nullptr) {
-      tp = idx % gl.dq_pairs_per_unit;
-      idx /= gl.dq_pairs_per_unit;
-      b = idx % g.batch;
-      hu = idx / g.batch;
-      sq = g.seqlen_q, sk = g.seqlen_k;
-      n_row_tiles = g.row_tiles;
-      tile_base = b * g.row_tiles;
-      if (g.causal) tp = gl.dq_pairs_per_unit - 1 - tp;  // heaviest first
-    } else {
-      hu = idx / gl.dq_pairs_per_unit;
-      const int r = idx - hu * gl.dq_pairs_per_unit;
-      int acc_p = 0, acc_r = 0;
-      b = -1;
-      for (int i = 0; i < g.batch; ++i) {
-        const int q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
-        const int nrt = (q1 - q0 + ppp - 1) / ppp, np = (nrt + 1) / 2;
-        if (r < acc_p + np) {
-          b = i, tp = r - acc_p, sq = q1 - q0, q_off = q0, n_row_tiles = nrt;
-          k_off = g.cu_k[i];
-          sk = g.cu_k[i + 1] - k_off;
-          if (g.causal) tp = np - 1 - tp;
-          break;
-        }
-        acc_p += np;
-        acc_r += nrt;
-      }
-      if (b < 0) return;
-      tile_base = acc_r;
-    }
-    if (hu >= g.head_units) return;
-    kvh = folded ? hu : hu / g.group;
-    // key extent written for this tile pair = that of its last tile, in 256-key blocks
-    const int t_last = min(2 * tp + 1, n_row_tiles - 1);
-    int kv_hi = sk;
-    if (g.causal) kv_hi = min(kv_hi, min((t_last + 1) * ppp, sq) + sk - sq);
-    n_stages = kv_hi > 0 ? ((kv_hi + 255) / 256) * 4 : 0;  // 64-key chunks
-  }
+  // optional cycle counters of one pair (debug[8..15]): where the MMA issuer and one epilogue warp wait
+  const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -160,6 +182,8 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
       mbar_init(ctrl + kBarEmpty + 8 * s, 1);
     }
     mbar_init(ctrl + kBarAccDone, 1);
+    mbar_init(ctrl + kBarAccFree, 16);  // 8 epilogue warps x 2 CTAs
+    tq_init(ctrl + kTileQ, kConsumers);
     fence_mbar_init();
     prefetch_tmap(&tm_ws);
   }
@@ -172,142 +196,219 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  // dQ: the row tile this CTA owns (clamped for loads when the last pair has a single tile)
-  const int my_tile = 2 * tp + rank;
-  const int my_tile_ld = min(my_tile, n_row_tiles - 1);
+  const uint32_t leader_acc_free = mapa_u32(ctrl + kBarAccFree, 0);
+  const TileQueue tq = tq_make(ctrl + kTileQ);
+  const int total_tiles = gl.n_kv_pairs + gl.n_dq_pairs;
+  GradTile t;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
       uint32_t it = 0;
+      const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0);
       auto acquire = [&](uint32_t& st, uint32_t& bar) {
         const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
         ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
         if (!ok) return;
         if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
-        bar = mapa_u32(ctrl + kBarFull + 8 * s, 0);
+        bar = leader_full0 + 8 * s;
         st = sRing + s * kStageBytes;
         ++it;
       };
-      if (mode != kModeDQ) {
-        const CUtensorMap* tm_b = mode == kModeDK ? &tm_q : &tm_do;
-        const int qb = g.cu_q ? 0 : b;
-        const int key0 = kt * 256 + rank * 128;
-        for (int u = 0; u < units && ok; ++u) {
-          const int h = folded ? kvh : kvh * g.group + u;
-          for (int t = t_min; t < n_row_tiles && ok; ++t) {
-            for (int c = 0; c < 2 && ok; ++c) {
-              uint32_t st = 0, bar = 0;
-              acquire(st, bar);
-              if (!ok) break;
-              const int ws_row = (tile_base + t) * kRowsPerPair + c * kRowsPerCta;
-              tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, h * 2 + mode);
-              tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, h * 2 + mode);
-              const int pos = q_off + t * ppp + c * g.pos_per_cta;
+      for (int n = 0; ok; ++n) {
+        const int idx = tq_fetch(tq, n, false, abort_flag, p.status);
+        if (idx < 0 || idx >= total_tiles) break;
+        if (!grad_decode(p, gl, idx, t) || t.n_stages == 0) continue;
+        if (t.mode != kModeDQ) {
+          const CUtensorMap* tm_b = t.mode == kModeDK ? &tm_q : &tm_do;
+          const int qb = g.cu_q ? 0 : t.b;
+          const int key0 = t.kt * 256 + rank * 128;
+          for (int u = 0; u < t.units && ok; ++u) {
+            const int h = folded ? t.kvh : t.kvh * g.group + u;
+            // last row tile first: under a causal mask the tiles of one KV head start at different rows, and
+            // walking down from the common end keeps the pairs that run side by side on the same Q / dO rows
+            for (int rt = t.n_row_tiles - 1; rt >= t.t_min && ok; --rt) {
+              for (int c = 0; c < 2 && ok; ++c) {
+                uint32_t st = 0, bar = 0;
+                acquire(st, bar);
+                if (!ok) break;
+                const int ws_row = (t.tile_base + rt) * kRowsPerPair + c * kRowsPerCta;
+                tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, h * 2 + t.mode);
+                tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, h * 2 + t.mode);
+                const int pos = t.q_off + rt * ppp + c * g.pos_per_cta;
 #pragma unroll
-              for (int m = 0; m < 2; ++m) {
-                const int d0 = m * 256 + rank * 128;
-                tma_load_5d_pair(st + 16384 + m * 16384, tm_b, bar, d0, 0, pos, h, qb);
-                tma_load_5d_pair(st + 16384 + m * 16384 + 8192, tm_b, bar, d0 + 64, 0, pos, h, qb);
+                for (int m = 0; m < 2; ++m) {
+                  const int d0 = m * 256 + rank * 128;
+                  tma_load_5d_pair(st + 16384 + m * 16384, tm_b, bar, d0, 0, pos, h, qb);
+                  tma_load_5d_pair(st + 16384 + m * 16384 + 8192, tm_b, bar, d0 + 64, 0, pos, h, qb);
+                }
               }
             }
           }
-        }
-      } else {
-        const int kb = g.cu_k ? 0 : b;
-        const int ws_row = (tile_base + my_tile_ld) * kRowsPerPair;
-        for (int c = 0; c < n_stages && ok; ++c) {
-          uint32_t st = 0, bar = 0;
-          acquire(st, bar);
-          if (!ok) break;
-          tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, hu * 2 + 1);
-          tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, hu * 2 + 1);
+        } else {
+          const int kb = g.cu_k ? 0 : t.b;
+          const int my_tile_ld = min(2 * t.tp + rank, t.n_row_tiles - 1);  // clamped when the last pair has one tile
+          const int ws_row = (t.tile_base + my_tile_ld) * kRowsPerPair;
+          for (int c = 0; c < t.n_stages && ok; ++c) {
+            uint32_t st = 0, bar = 0;
+            acquire(st, bar);
+            if (!ok) break;
+            tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, t.hu * 2 + 1);
+            tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, t.hu * 2 + 1);
 #pragma unroll
-          for (int m = 0; m < 2; ++m) {
-            const int d0 = m * 256 + rank * 128;
-            tma_load_4d_pair(st + 16384 + m * 16384, &tm_k, bar, d0, k_off + c * 64, kvh, kb);
-            tma_load_4d_pair(st + 16384 + m * 16384 + 8192, &tm_k, bar, d0 + 64, k_off + c * 64, kvh, kb);
+            for (int m = 0; m < 2; ++m) {
+              const int d0 = m * 256 + rank * 128;
+              tma_load_4d_pair(st + 16384 + m * 16384, &tm_k, bar, d0, t.k_off + c * 64, t.kvh, kb);
+              tma_load_4d_pair(st + 16384 + m * 16384 + 8192, &tm_k, bar, d0 + 64, t.k_off + c * 64, t.kvh, kb);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
-    if (rank == 0 && lane == 0 && n_stages > 0) {
-      const uint32_t idesc = make_idesc(false, mode != kModeDQ, true, 256, 256);
-      const uint32_t a_step = mode != kModeDQ ? 2048u : 32u;   // 16 contraction elements further
-      const uint32_t a_lbo = mode != kModeDQ ? 8192u : 16u;
+    if (rank == 0 && lane == 0) {
       bool ok = true;
-      for (int it = 0; it < n_stages && ok; ++it) {
-        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-        ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t st = sRing + s * kStageBytes;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t da = make_desc_sw128(st + k * a_step, a_lbo, 1024);
-#pragma unroll
-          for (int m = 0; m < 2; ++m) {
-            const uint64_t db = make_desc_sw128(st + 16384 + m * 16384 + k * 2048, 8192, 1024);
-            umma_ss<2>(tmem_base + m * 256, da, db, idesc, (it | k) != 0);
-          }
+      uint32_t it = 0;
+      int tiles = 0;
+      long long t_full = 0, t_free = 0;
+      const long long t_begin = prof ? clock64() : 0;
+      for (int n = 0; ok; ++n) {
+        const int idx = tq_fetch(tq, n, false, abort_flag, p.status);
+        if (idx < 0 || idx >= total_tiles) break;
+        if (!grad_decode(p, gl, idx, t) || t.n_stages == 0) continue;
+        const bool kv = t.mode != kModeDQ;
+        const uint32_t idesc = make_idesc(false, kv, true, 256, 256);
+        const uint32_t a_step = kv ? (2048u >> 4) : (32u >> 4);  // 16 contraction elements further
+        const uint32_t a_lbo = kv ? 8192u : 16u;
+        if (tiles > 0) {  // the previous tile's epilogue must have drained the accumulator
+          const long long t0 = prof ? clock64() : 0;
+          ok = mbar_wait<true>(ctrl + kBarAccFree, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_free += clock64() - t0;
         }
-        umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+        for (int c = 0; c < t.n_stages && ok; ++c) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
+          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof) t_full += clock64() - t0;
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t st = sRing + s * kStageBytes;
+          const uint32_t a0 = desc_lo(st, a_lbo), b0 = desc_lo(st + 16384, 8192);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+              umma_ss<2>(tmem_base + m * 256, desc_join(a0 + k * a_step),
+                         desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc, (c | k) != 0);
+          }
+          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          ++it;
+        }
+        if (ok) umma_commit_pair(ctrl + kBarAccDone, 3);
+        ++tiles;
       }
-      if (ok) umma_commit_pair(ctrl + kBarAccDone, 3);
+      if (prof) {
+        p.debug[8] = static_cast<float>(clock64() - t_begin);
+        p.debug[9] = static_cast<float>(t_full);
+        p.debug[10] = static_cast<float>(t_free);
+        p.debug[11] = static_cast<float>(it);
+        p.debug[12] = static_cast<float>(tiles);
+      }
     }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ tile scheduler (leader CTA)
+    if (rank == 0 && lane == 0)
+      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterGrad, pair_id, n_pairs, total_tiles, abort_flag, p.status);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue: TMEM -> bf16 -> global
-    const int q = warp & 3;
-    const int L = q * 32 + lane;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    // 8 warps: warp & 3 selects the 32 TMEM lanes (output rows), (warp - 4) / 4 the 256-column half.
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    const int Lr = q * 32 + (lane & ~3);      // after the transpose it stores rows Lr .. Lr + 3
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 256;
     bool ok = true;
-    if (n_stages > 0) {
-      ok = mbar_wait(ctrl + kBarAccDone, 0, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-      ok = __all_sync(0xffffffffu, ok);
-      tc_fence_after_sync();
-    }
-    if (ok) {
-      uint16_t* drow = nullptr;
-      bool store = false;
-      if (mode != kModeDQ) {
-        const int key = kt * 256 + rank * 128 + L;
-        uint16_t* base = reinterpret_cast<uint16_t*>(mode == kModeDK ? p.dk : p.dv);
-        const int64_t sb = mode == kModeDK ? p.dk_stride_b : p.dv_stride_b;
-        const int64_t ss = mode == kModeDK ? p.dk_stride_s : p.dv_stride_s;
-        const int64_t sh = mode == kModeDK ? p.dk_stride_h : p.dv_stride_h;
-        drow = base + (g.cu_q ? 0 : b * sb) + static_cast<int64_t>(k_off + key) * ss + kvh * sh;
-        store = key < sk;
-      } else {
-        const int pos = my_tile * ppp + L / g.pack_g;
-        const int head = g.pack_g > 1 ? hu * g.pack_g + L % g.pack_g : hu;
-        drow = reinterpret_cast<uint16_t*>(p.dq) + (g.cu_q ? 0 : b * p.dq_stride_b) +
-               static_cast<int64_t>(q_off + pos) * p.dq_stride_s + static_cast<int64_t>(head) * p.dq_stride_h;
-        store = my_tile < n_row_tiles && pos < sq;
+    int tiles = 0;
+    long long t_done = 0, t_drain = 0;
+    const long long t_begin = prof ? clock64() : 0;
+    for (int n = 0; ok; ++n) {
+      const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
+      if (idx < 0 || idx >= total_tiles) break;
+      if (!grad_decode(p, gl, idx, t)) continue;
+      const bool live = t.n_stages > 0;
+      const long long t0 = prof ? clock64() : 0;
+      if (live) {
+        ok = mbar_wait(ctrl + kBarAccDone, tiles & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
       }
-      uint32_t r[32];
+      const long long t1 = prof ? clock64() : 0;
+      t_done += t1 - t0;
+      // destination rows of the four rows this thread stores (chunk lane & 3 of each)
+      uint16_t* drow[4];
+      bool store[4];
+      if (t.mode != kModeDQ) {
+        uint16_t* base = reinterpret_cast<uint16_t*>(t.mode == kModeDK ? p.dk : p.dv);
+        const int64_t sb = t.mode == kModeDK ? p.dk_stride_b : p.dv_stride_b;
+        const int64_t ss = t.mode == kModeDK ? p.dk_stride_s : p.dv_stride_s;
+        const int64_t sh = t.mode == kModeDK ? p.dk_stride_h : p.dv_stride_h;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = t.kt * 256 + rank * 128 + Lr + j;
+          drow[j] = base + (g.cu_q ? 0 : t.b * sb) + static_cast<int64_t>(t.k_off + key) * ss + t.kvh * sh;
+          store[j] = key < t.sk;
+        }
+      } else {
+        const int my_tile = 2 * t.tp + rank;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = Lr + j;
+          const int pos = my_tile * ppp + row / g.pack_g;
+          const int head = g.pack_g > 1 ? t.hu * g.pack_g + row % g.pack_g : t.hu;
+          drow[j] = reinterpret_cast<uint16_t*>(p.dq) + (g.cu_q ? 0 : t.b * p.dq_stride_b) +
+                    static_cast<int64_t>(t.q_off + pos) * p.dq_stride_s + static_cast<int64_t>(head) * p.dq_stride_h;
+          store[j] = my_tile < t.n_row_tiles && pos < t.sq;
+        }
+      }
 #pragma unroll 1
-      for (int c = 0; c < 16; ++c) {
-        if (n_stages > 0) {
-          tmem_ld32(lane_addr + c * 32, r);
+      for (int c = 0; c < 4; ++c) {  // 64 accumulator columns per step
+        uint32_t x[32];
+        if (live) {
+          uint32_t a[32], b[32];
+          tmem_ld32(lane_addr + c * 64, a);
+          tmem_ld32(lane_addr + c * 64 + 32, b);
           tmem_ld_wait();
+          if (c == 3) {  // accumulator read: the next tile's first MMA may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_free);
+            if (prof) t_drain += clock64() - t1;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            x[i] = pack2<false>(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
+            x[16 + i] = pack2<false>(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]));
+          }
+          // 64 columns x 2 bytes = 4 chunks of 32 bytes of this thread's row; after the transpose the thread
+          // holds chunk (lane & 3) of rows Lr .. Lr + 3, so each 256-bit store instruction of the warp writes
+          // whole 128-byte lines
+          transpose_chunks32_4x4(x, lane);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 32; ++i) x[i] = 0u;
         }
-        if (store) {
+        const int col = half * 256 + c * 64 + (lane & 3) * 16;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t)
-              w[t] = pack2<false>(__uint_as_float(r[i + 2 * t]), __uint_as_float(r[i + 2 * t + 1]));
-            st_global_v4(drow + c * 32 + i, w[0], w[1], w[2], w[3]);
-          }
-        }
+        for (int j = 0; j < 4; ++j)
+          if (store[j]) st_global_32b(drow[j] + col, &x[8 * j]);
       }
+      if (live) ++tiles;
+    }
+    if (prof && warp == 4 && lane == 0) {
+      p.debug[13] = static_cast<float>(clock64() - t_begin);
+      p.debug[14] = static_cast<float>(t_done);
+      p.debug[15] = static_cast<float>(t_drain);
     }
   }
 
@@ -356,8 +457,14 @@ int launch_bwd_grad(const splitd_params* p, cudaStream_t stream, int modes) {
   cudaError_t ce =
       cudaFuncSetAttribute(splitd_bwd_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, grad::kSmemBytes);
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(grad): %s", cudaGetErrorString(ce));
-  splitd_bwd_grad_kernel<<<dim3(static_cast<unsigned>(2 * pairs)), dim3(256), grad::kSmemBytes, stream>>>(
-      tm_ws, tm_do, tm_q, tm_k, bp, gl);
+  // persistent: as many CTA pairs as the device keeps resident at once
+  static int cache[64] = {};
+  const int resident = resident_cluster_pairs(splitd_bwd_grad_kernel, grad::kThreads, grad::kSmemBytes, cache);
+  const long long grid_pairs = pairs < resident ? pairs : resident;
+  ce = cudaMemsetAsync(bp.tile_counters + kCounterGrad, 0, sizeof(int), stream);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
+  splitd_bwd_grad_kernel<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(grad::kThreads), grad::kSmemBytes,
+                           stream>>>(tm_ws, tm_do, tm_q, tm_k, bp, gl);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "gradient GEMM launch failed: %s", cudaGetErrorString(ce));
   return 0;

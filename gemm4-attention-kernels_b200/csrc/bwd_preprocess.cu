@@ -74,7 +74,7 @@ size_t bwd_workspace_bytes(const splitd_params* p) {
   fill_geom(p, g);
   int64_t rows, pitch;
   ws_shape(p, g, rows, pitch);
-  return static_cast<size_t>(2) * g.head_units * rows * pitch * sizeof(uint16_t);
+  return static_cast<size_t>(2) * g.head_units * rows * pitch * sizeof(uint16_t) + kWsCounterBytes;
 }
 
 int fill_bwd_params(const splitd_params* p, BwdParams& bp) {
@@ -105,6 +105,9 @@ int fill_bwd_params(const splitd_params* p, BwdParams& bp) {
       return fail(SPLITD_ERR_INVALID_ARGUMENT, "o/dout/dq/dk/dv must be 16-byte aligned");
   bp.ws = reinterpret_cast<uint16_t*>(p->workspace);
   ws_shape(p, g, bp.ws_rows, bp.ws_pitch);
+  if (p->workspace)  // the counters sit behind the tiles
+    bp.tile_counters = reinterpret_cast<int*>(static_cast<uint8_t*>(p->workspace) +
+                                              static_cast<size_t>(2) * g.head_units * bp.ws_rows * bp.ws_pitch * sizeof(uint16_t));
   bp.total_q = p->total_q;
   bp.total_k = p->total_k;
   const bool varlen = p->cu_seqlens_q != nullptr;

@@ -71,7 +71,10 @@ struct BwdParams {
   float scale_log2, scale;
   int* status;
   float* debug;           // optional per-role cycle counters (tests / tuning only)
+  int* tile_counters;     // kWsCounterBytes at the end of the workspace: work counters of the persistent kernels
 };
+constexpr int kWsCounterBytes = 256;
+constexpr int kCounterPds = 0, kCounterGrad = 32;  // int offsets, 128 bytes apart
 
 // Which tile does this CTA pair work on. Returns false when the pair has nothing to do.
 struct TileCoord {

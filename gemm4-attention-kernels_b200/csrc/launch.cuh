@@ -30,4 +30,33 @@ size_t bwd_workspace_bytes(const splitd_params* p);
 int fill_bwd_params(const splitd_params* p, BwdParams& bp);
 int check_workspace(const splitd_params* p);
 
+// Number of 2-CTA clusters of `kern` the current device keeps resident at once (the grid of a persistent
+// kernel). `cache` holds one entry per device index and is filled on first use.
+template <typename Kernel>
+inline int resident_cluster_pairs(Kernel kern, int threads, int smem_bytes, int (&cache)[64]) {
+  int dev = 0, resident = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  cudaError_t ce = cudaOccupancyMaxActiveClusters(&resident, kern, &cfg);
+  if (ce != cudaSuccess || resident <= 0) {
+    cudaGetLastError();
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    resident = sms > 1 ? sms / 2 : 1;
+  }
+  if (dev >= 0 && dev < 64) cache[dev] = resident;
+  return resident;
+}
+
 }  // namespace sd

@@ -421,5 +421,14 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
                "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                : "memory");
 }
+// 32 bytes to an address that is only known to be 16-byte aligned: one 256-bit store when it can be.
+__device__ __forceinline__ void st_global_32b(void* p, const uint32_t* w) {
+  if ((reinterpret_cast<uintptr_t>(p) & 31u) == 0) {
+    st_global_v8(p, w);
+  } else {
+    st_global_v4(p, w[0], w[1], w[2], w[3]);
+    st_global_v4(static_cast<uint8_t*>(p) + 16, w[4], w[5], w[6], w[7]);
+  }
+}
 
 }  // namespace sd

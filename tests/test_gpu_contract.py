@@ -119,5 +119,5 @@ def test_c_abi_rejects_missing_workspace():
     p.dpsum = p.lse_log2 = ctypes.c_void_p(stat.data_ptr())
     p.do_strides[:] = p.dq_strides[:] = p.dk_strides[:] = p.dv_strides[:] = I._strides3(g, False)
     lib = _capi.load_library()
-    assert lib.splitd_bwd_workspace_bytes(ctypes.byref(p)) == 2 * 2 * 128 * (256 + 64) * 2
+    assert lib.splitd_bwd_workspace_bytes(ctypes.byref(p)) == 2 * 2 * 128 * (256 + 64) * 2 + 256  # tiles + work counters
     assert lib.splitd_bwd_dq(ctypes.byref(p), None) == -5
