@@ -252,17 +252,21 @@ def run_ours(args):
     achieved = algo[dom] * n_steps / kt[dom] / 1e9
     n_launch = len(cases)
     traffic = None if dram_bytes_per_flop[dom] is None else dram_bytes_per_flop[dom] * algo[dom] / n_launch
-    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "traffic_note": "avg DRAM bytes per launch, scaled from an ncu capture",
-                "peak_source": f"{peak_kind} bf16 burst",
+    # The kernels are timed back to back inside a step of ~0.2 s that runs under the power cap, so the
+    # denominator is the sustained cuBLAS figure; the burst figure (a kernel timed alone) is given beside it.
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_sus, "unit": "TFLOP/s",
+                "frac": achieved / peak_sus, "traffic": traffic, "traffic_note": "avg DRAM bytes per launch, scaled from an ncu capture",
+                "peak_source": f"{peak_kind} bf16 sustained (kernel timed inside a long step under sw_power_cap)",
+                "peak_burst": peak, "frac_of_burst": achieved / peak,
                 "per_kernel_tflops": {n: algo[n] * n_steps / kt[n] / 1e9 for n in algo},
                 "per_kernel_ms_per_step": {n: kt[n] / n_steps for n in kt}}
 
     # ---- end to end through the public API with host buffers
     pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
     hq_, hk_, hv_, hdo_ = pin(q), pin(k), pin(v), pin(do)
-    ho, hdq = torch.empty_like(hq_), torch.empty_like(hq_)
-    hdk, hdv = torch.empty_like(hk_), torch.empty_like(hk_)
+    pinned_like = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)  # empty_like would be pageable
+    ho, hdq = pinned_like(hq_), pinned_like(hq_)
+    hdk, hdv = pinned_like(hk_), pinned_like(hk_)
     h2d = (hq_.numel() + hk_.numel() + hv_.numel() + hdo_.numel()) * 2 * len(cases)
     d2h = (ho.numel() + hdq.numel() + hdk.numel() + hdv.numel()) * 2 * len(cases)
 
