@@ -8,8 +8,9 @@
 // Query-stationary CTA pair, cta_group::2 UMMAs with M = 128 (64 packed rows per CTA), N = 256 keys per
 // step. No accumulator lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns:
 // the tensor pipe fills one pair while eight element-wise warps drain the other. Q and dO (64 x 512 each)
-// stay in shared memory; K and V rows stream through a 3 x 32 KB ring (8 MMAs per barrier round trip:
-// one thread issues a tcgen05.mma every ~45 cycles at best and each of these runs for 64).
+// stay in shared memory; K rows and V rows stream through two rings of 3 x 16 KB, one per issuing thread
+// (one thread issues a tcgen05.mma every ~45 cycles at best, these run for 64, and the barrier round trips
+// of a stage come on top: two independent issue streams keep the tensor pipe fed).
 // A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
 // the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
 // fully masked and therefore zero.
@@ -23,17 +24,20 @@ namespace sd {
 
 namespace pds {
 constexpr int kStepKeys = 256;
-constexpr int kStages = 3;
-constexpr int kStageBytes = 32768;
+constexpr int kStages = 3;            // per ring; one ring for K rows, one for V rows
+constexpr int kStageBytes = 16384;    // one TMA box: this CTA's 128 keys x 64 of the 512 D columns
 constexpr int kOffQ = 0;
 constexpr int kOffDO = 65536;
-constexpr int kOffRing = 131072;
-constexpr int kOffCtrl = kOffRing + kStages * kStageBytes;
+constexpr int kOffRingK = 131072;
+constexpr int kOffRingV = kOffRingK + kStages * kStageBytes;
+constexpr int kOffCtrl = kOffRingV + kStages * kStageBytes;
 constexpr int kBarQFull = 0;
-constexpr int kBarFull = 8;
-constexpr int kBarEmpty = kBarFull + 8 * kStages;
-constexpr int kBarSdpFull = kBarEmpty + 8 * kStages;  // [2]
-constexpr int kBarSdpFree = kBarSdpFull + 16;         // [2], leader CTA only
+constexpr int kBarFullK = 8;
+constexpr int kBarEmptyK = kBarFullK + 8 * kStages;
+constexpr int kBarFullV = kBarEmptyK + 8 * kStages;
+constexpr int kBarEmptyV = kBarFullV + 8 * kStages;
+constexpr int kBarSdpFull = kBarEmptyV + 8 * kStages;  // [2], two arrivals each: the S issuer's and the dP issuer's commit
+constexpr int kBarSdpFree = kBarSdpFull + 16;          // [2], leader CTA only
 constexpr int kTmemPtr = kBarSdpFree + 16;
 constexpr int kAbort = kTmemPtr + 4;
 constexpr int kCtrlBytes = 256;
@@ -53,7 +57,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     return;
   }
   const uint32_t sQ = smem_base + kOffQ, sDO = smem_base + kOffDO;
-  const uint32_t sRing = smem_base + kOffRing, ctrl = smem_base + kOffCtrl;
+  const uint32_t sRingK = smem_base + kOffRingK, sRingV = smem_base + kOffRingV, ctrl = smem_base + kOffCtrl;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
 
@@ -82,11 +86,13 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     *abort_flag = 0;
     mbar_init(ctrl + kBarQFull, 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(ctrl + kBarFull + 8 * s, 1);
-      mbar_init(ctrl + kBarEmpty + 8 * s, 1);
+      mbar_init(ctrl + kBarFullK + 8 * s, 1);
+      mbar_init(ctrl + kBarEmptyK + 8 * s, 1);
+      mbar_init(ctrl + kBarFullV + 8 * s, 1);
+      mbar_init(ctrl + kBarEmptyV + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(ctrl + kBarSdpFull + 8 * b, 1);
+      mbar_init(ctrl + kBarSdpFull + 8 * b, 2);
       mbar_init(ctrl + kBarSdpFree + 8 * b, 16);  // 8 element-wise warps x 2 CTAs
     }
     fence_mbar_init();
@@ -116,62 +122,69 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
       }
       const int kb = g.cu_k ? 0 : tc.b;
+      const uint32_t leader_full_k = mapa_u32(ctrl + kBarFullK, 0), leader_full_v = mapa_u32(ctrl + kBarFullV, 0);
       uint32_t it = 0;
       bool ok = true;
       for (int j = 0; j < n_steps && ok; ++j) {
         const int key0 = tc.k_off + j * kStepKeys + static_cast<int>(rank) * 128;
-        for (int c = 0; c < 8 && ok; ++c) {  // 4 stages of K then 4 of V, 128 of the 512 D columns each
+        for (int c = 0; c < 8 && ok; ++c) {  // K and V boxes alternate so that both issuers are fed evenly
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          ok = mbar_wait(ctrl + kBarEmptyK + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
           if (!ok) break;
-          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
-          const CUtensorMap* tm = c < 4 ? &tm_k : &tm_v;
-          const uint32_t bar = mapa_u32(ctrl + kBarFull + 8 * s, 0);
-          tma_load_4d_pair(sRing + s * kStageBytes, tm, bar, (2 * (c & 3)) * 64, key0, tc.hkv, kb);
-          tma_load_4d_pair(sRing + s * kStageBytes + 16384, tm, bar, (2 * (c & 3) + 1) * 64, key0, tc.hkv, kb);
+          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullK + 8 * s, 2 * kStageBytes);
+          tma_load_4d_pair(sRingK + s * kStageBytes, &tm_k, leader_full_k + 8 * s, c * 64, key0, tc.hkv, kb);
+          ok = mbar_wait(ctrl + kBarEmptyV + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          if (!ok) break;
+          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullV + 8 * s, 2 * kStageBytes);
+          tma_load_4d_pair(sRingV + s * kStageBytes, &tm_v, leader_full_v + 8 * s, c * 64, key0, tc.hkv, kb);
           ++it;
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 2) {
+    // Two issuing threads: warp 1 issues the S = Q K^T MMAs from the K ring, warp 2 the dP = dO V^T MMAs from
+    // the V ring. One thread cannot issue 64-cycle MMAs (M = 128) back to back once barrier waits and commits
+    // are added; two independent instruction streams keep the tensor pipe busy.
     if (rank == 0 && lane == 0 && n_steps > 0) {
+      const bool is_s = warp == 1;
       constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
-      const uint32_t q_lo = desc_lo(sQ, 16), do_lo = desc_lo(sDO, 16), ring_lo = desc_lo(sRing, 16);
+      const uint32_t a_lo = desc_lo(is_s ? sQ : sDO, 16), ring_lo = desc_lo(is_s ? sRingK : sRingV, 16);
+      const uint32_t bar_full = ctrl + (is_s ? kBarFullK : kBarFullV), bar_empty = ctrl + (is_s ? kBarEmptyK : kBarEmptyV);
+      const uint32_t d_off = is_s ? 0 : 128;
+      const bool prof_t = prof && is_s;
       uint32_t it = 0;
-      t_all = prof ? clock64() : 0;
+      t_all = prof_t ? clock64() : 0;
       bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       tc_fence_after_sync();
       for (int j = 0; j < n_steps && ok; ++j) {
         const int b = j & 1;
         if (j >= 2) {  // buffer pair b must have been drained
-          const long long t0 = prof ? clock64() : 0;
+          const long long t0 = prof_t ? clock64() : 0;
           ok = mbar_wait<true>(ctrl + kBarSdpFree + 8 * b, ((j >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
-          if (prof) t_b += clock64() - t0;
+          if (prof_t) t_b += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
         }
+        const uint32_t d_tmem = tmem_base + b * 256 + d_off;
 #pragma unroll 1
         for (int c = 0; c < 8 && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          const long long t0 = prof ? clock64() : 0;
-          ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
-          if (prof) t_a += clock64() - t0;
+          const long long t0 = prof_t ? clock64() : 0;
+          ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          if (prof_t) t_a += clock64() - t0;
           if (!ok) break;
-          const uint32_t a0 = (c < 4 ? q_lo : do_lo) + (c & 3) * (16384 >> 4);
+          tc_fence_after_sync();
+          const uint32_t a0 = a_lo + c * (8192 >> 4);
           const uint32_t b0 = ring_lo + s * (kStageBytes >> 4);
-          const uint32_t d_tmem = tmem_base + b * 256 + (c < 4 ? 0 : 128);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;
-            const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;
-            umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc, ((c & 3) | k) != 0);
-          }
-          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          for (int k = 0; k < 4; ++k)
+            umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
+          umma_commit_pair(bar_empty + 8 * s, 3);
           ++it;
         }
         if (ok) umma_commit_pair(ctrl + kBarSdpFull + 8 * b, 3);
       }
-      if (prof) {
+      if (prof_t) {
         p.debug[0] = static_cast<float>(t_a);
         p.debug[1] = static_cast<float>(t_b);
         p.debug[2] = static_cast<float>(clock64() - t_all);
