@@ -268,14 +268,16 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
-    if (rank == 0 && lane == 0) {
+    // The whole warp runs the loop, one elected lane issues (warp-uniform control flow keeps the cost of
+    // waits, descriptor adds and commits well below the 128 cycles one of these MMAs runs for).
+    if (rank == 0) {
       bool ok = true;
       uint32_t it = 0;
       int tiles = 0;
       long long t_full = 0, t_free = 0;
       const long long t_begin = prof ? clock64() : 0;
       for (int n = 0; ok; ++n) {
-        const int idx = tq_fetch(tq, n, false, abort_flag, p.status);
+        const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
         if (idx < 0 || idx >= total_tiles) break;
         if (!grad_decode(p, gl, idx, t) || t.n_stages == 0) continue;
         const bool kv = t.mode != kModeDQ;
@@ -285,31 +287,36 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
         if (tiles > 0) {  // the previous tile's epilogue must have drained the accumulator
           const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait<true>(ctrl + kBarAccFree, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
           if (prof) t_free += clock64() - t0;
         }
         for (int c = 0; c < t.n_stages && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           const long long t0 = prof ? clock64() : 0;
           ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
           if (prof) t_full += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t st = sRing + s * kStageBytes;
           const uint32_t a0 = desc_lo(st, a_lbo), b0 = desc_lo(st + 16384, 8192);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < 4; ++k) {
 #pragma unroll
-            for (int m = 0; m < 2; ++m)
-              umma_ss<2>(tmem_base + m * 256, desc_join(a0 + k * a_step),
-                         desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc, (c | k) != 0);
+              for (int m = 0; m < 2; ++m)
+                umma_ss<2>(tmem_base + m * 256, desc_join(a0 + k * a_step),
+                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc, (c | k) != 0);
+            }
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            if (c == t.n_stages - 1) umma_commit_pair(ctrl + kBarAccDone, 3);
           }
-          umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+          __syncwarp();
           ++it;
         }
-        if (ok) umma_commit_pair(ctrl + kBarAccDone, 3);
         ++tiles;
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.debug[8] = static_cast<float>(clock64() - t_begin);
         p.debug[9] = static_cast<float>(t_full);
         p.debug[10] = static_cast<float>(t_free);

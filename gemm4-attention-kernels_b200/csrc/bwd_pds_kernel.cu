@@ -9,8 +9,7 @@
 // step. No accumulator lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns:
 // the tensor pipe fills one pair while eight element-wise warps drain the other. Q and dO (64 x 512 each)
 // stay in shared memory; K rows and V rows stream through two rings of 3 x 16 KB, one per issuing thread
-// (one thread issues a tcgen05.mma every ~45 cycles at best, these run for 64, and the barrier round trips
-// of a stage come on top: two independent issue streams keep the tensor pipe fed).
+// (two independent issue streams and finer stages keep more of the K/V stream in flight).
 // A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
 // the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
 // fully masked and therefore zero.
@@ -142,10 +141,12 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
     }
   } else if (warp == 1 || warp == 2) {
-    // Two issuing threads: warp 1 issues the S = Q K^T MMAs from the K ring, warp 2 the dP = dO V^T MMAs from
-    // the V ring. One thread cannot issue 64-cycle MMAs (M = 128) back to back once barrier waits and commits
-    // are added; two independent instruction streams keep the tensor pipe busy.
-    if (rank == 0 && lane == 0 && n_steps > 0) {
+    // Two issuing warps: warp 1 issues the S = Q K^T MMAs from the K ring, warp 2 the dP = dO V^T MMAs from
+    // the V ring, so each GEMM has its own instruction stream and its own operand prefetch. In each the whole
+    // warp runs the loop and one elected lane issues: warp-uniform control flow makes waits, descriptor adds
+    // and commits cost ~42 cycles per MMA instead of ~85 for a single lane under a divergent branch (both
+    // measured), which is what keeps the 64-cycle MMAs of this shape back to back.
+    if (rank == 0 && n_steps > 0) {
       const bool is_s = warp == 1;
       constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
       const uint32_t a_lo = desc_lo(is_s ? sQ : sDO, 16), ring_lo = desc_lo(is_s ? sRingK : sRingV, 16);
@@ -155,12 +156,14 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       uint32_t it = 0;
       t_all = prof_t ? clock64() : 0;
       bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
       for (int j = 0; j < n_steps && ok; ++j) {
         const int b = j & 1;
         if (j >= 2) {  // buffer pair b must have been drained
           const long long t0 = prof_t ? clock64() : 0;
           ok = mbar_wait<true>(ctrl + kBarSdpFree + 8 * b, ((j >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
           if (prof_t) t_b += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
@@ -171,20 +174,24 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           const long long t0 = prof_t ? clock64() : 0;
           ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = __all_sync(0xffffffffu, ok);
           if (prof_t) t_a += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a0 = a_lo + c * (8192 >> 4);
           const uint32_t b0 = ring_lo + s * (kStageBytes >> 4);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
-          umma_commit_pair(bar_empty + 8 * s, 3);
+            for (int k = 0; k < 4; ++k)
+              umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
+            umma_commit_pair(bar_empty + 8 * s, 3);
+            if (c == 7) umma_commit_pair(ctrl + kBarSdpFull + 8 * b, 3);
+          }
+          __syncwarp();
           ++it;
         }
-        if (ok) umma_commit_pair(ctrl + kBarSdpFull + 8 * b, 3);
       }
-      if (prof_t) {
+      if (prof_t && lane == 0) {
         p.debug[0] = static_cast<float>(t_a);
         p.debug[1] = static_cast<float>(t_b);
         p.debug[2] = static_cast<float>(clock64() - t_all);

@@ -8,8 +8,8 @@
 //     S (64 x 256 keys) x 2  -> 2 buffers x 128 columns        = columns [256,512)
 // and the B operand of every MMA (K rows for QK^T, V columns for PV) is split between the two
 // CTAs, which halves the K/V bytes each SM pulls from L2.
-// (Measured: this 64-rows-per-CTA form computes a 64 x 256 x 16 MMA in 64 cycles, i.e. full rate, but with
-// both operands in shared memory the operand fetch path (~68 B/clk/SM) makes it ~88 cycles.)
+// (Measured: this 64-rows-per-CTA form runs a 64 x 256 x 16 MMA in 64 cycles, i.e. at full rate, provided
+// the issuing warp keeps up: see the MMA issuer below.)
 //
 // Per KV step of 256 keys:  S = Q K^T (32 MMAs, K-major operands)  ->  softmax warps: row max
 // (exchanged between the four threads that share a row), P = exp2(...) as bf16 into shared memory
@@ -233,10 +233,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA)
-    // One thread can issue a tcgen05.mma every ~45 cycles at best, so the loop is kept to a few
-    // instructions per MMA: descriptor low words are advanced by adding, the high word is a constant, and
-    // one barrier wait / commit covers 8 MMAs (a 32 KB stage).
-    if (rank == 0 && lane == 0) {
+    // The WHOLE warp runs this loop and one elected lane issues: with warp-uniform control flow the barrier
+    // waits, descriptor arithmetic and commits cost ~42 cycles per MMA, which keeps the 64-cycle MMAs of this
+    // shape back to back; the same loop run by a single lane under a divergent branch costs ~85 cycles per
+    // MMA (both measured). Descriptor low words are advanced by adding, the high word is a constant, and one
+    // barrier wait / commit covers 8 MMAs (a 32 KB stage).
+    if (rank == 0) {
       constexpr uint32_t idesc_s = make_idesc(kFp16, false, false, 128, kStepKeys);
       constexpr uint32_t idesc_pv = make_idesc(kFp16, false, true, 128, 256);
       const uint32_t p_lo = desc_lo(sP, 16);
@@ -249,6 +251,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       TileCoord tc;
       int step0, n_steps;
       bool valid;
+      // wait on a barrier with all lanes, keep the outcome warp-uniform
+      auto wait_all = [&](uint32_t bar, uint32_t parity, bool cluster_scope) {
+        bool w = cluster_scope ? mbar_wait<true>(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA)
+                               : mbar_wait(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA);
+        return __all_sync(0xffffffffu, w);
+      };
       for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid); ++r) {
         if (!valid || n_steps == 0) continue;
         // Q of this tile: wait for its two ring entries, hand the previous tile's Q slots to the ring
@@ -257,11 +265,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           uint32_t newq = 0;
           for (int u = 0; u < 2 && ok; ++u) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
             if (!ok) break;
             newq = slot_set(newq, u, slot_get(rs, s));
             rs = slot_set(rs, s, slot_get(qs, u));
-            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);  // old Q slot is free once all earlier MMAs are done
+            if (elect_one()) umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);  // old Q slot is free once all earlier MMAs are done
+            __syncwarp();
             ++it;
           }
           if (!ok) break;
@@ -275,52 +284,60 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int c = 0; c < 4 && ok; ++c) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
             const long long t0 = prof ? clock64() : 0;
-            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
             if (prof) t_a += clock64() - t0;
             if (!ok) break;
+            tc_fence_after_sync();
             const uint32_t a0 = (c < 2 ? q_lo[0] : q_lo[1]) + (((c & 1) * 16384) >> 4);
             const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 16);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;   // A: 8 KB per 64-wide D block
-              const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;  // B: 16 KB per 64-wide D block
-              umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc_s, (c | k) != 0);
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;   // A: 8 KB per 64-wide D block
+                const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;  // B: 16 KB per 64-wide D block
+                umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc_s, (c | k) != 0);
+              }
+              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+              if (c == 3) umma_commit_pair(ctrl + kBarSFull + 8 * (step & 1), 3);
             }
-            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            __syncwarp();
             ++it;
           }
-          if (ok) umma_commit_pair(ctrl + kBarSFull + 8 * (step & 1), 3);
         };
         auto issue_pv = [&](int j) {
 #pragma unroll 1
           for (int kq = 0; kq < 4 && ok; ++kq) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
             const long long t0 = prof ? clock64() : 0;
-            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
             if (prof) t_b += clock64() - t0;
             if (!ok) break;
+            tc_fence_after_sync();
             const uint32_t a0 = p_lo + kq * (8192 >> 4);
             const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 8192);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+              for (int k = 0; k < 4; ++k) {
 #pragma unroll
-              for (int m = 0; m < 2; ++m)
-                umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
-                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
+                for (int m = 0; m < 2; ++m)
+                  umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
+                             desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
+              }
+              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+              if (kq == 3) umma_commit_pair(ctrl + kBarPvDone, 3);
             }
-            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            __syncwarp();
             ++it;
           }
-          if (ok) umma_commit_pair(ctrl + kBarPvDone, 3);
         };
         issue_s(gs);
         for (int j = 0; j < n_steps && ok; ++j) {
           if (j + 1 < n_steps) issue_s(gs + 1);
           if (!ok) break;
           const long long t0 = prof ? clock64() : 0;
-          ok = mbar_wait<true>(ctrl + kBarPFull, gs & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          ok = wait_all(ctrl + kBarPFull, gs & 1, true);
           if (ok && j == 0 && tiles > 0)  // the previous tile's epilogue must have drained O
-            ok = mbar_wait<true>(ctrl + kBarOFree, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = wait_all(ctrl + kBarOFree, (tiles - 1) & 1, true);
           if (prof) t_c += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
@@ -329,7 +346,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         ++tiles;
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.debug[100002] = static_cast<float>(gs);
         p.debug[100004] = static_cast<float>(t_a);
         p.debug[100005] = static_cast<float>(t_b);
