@@ -389,7 +389,7 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
           if (c == 3) {  // accumulator read: the next tile's first MMA may overwrite it
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_acc_free);
+            if (lane == 0) mbar_arrive_remote(leader_acc_free);
             if (prof) t_drain += clock64() - t1;
           }
 #pragma unroll

@@ -371,6 +371,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     int step0, n_steps;
     bool valid;
     t_all = prof ? clock64() : 0;
+    long long tph0 = 0, tph1 = 0, tph2 = 0, tph3 = 0, tph4 = 0, tph5 = 0, tph6 = 0;
 
     for (int rr = 0; ok && fwd_next_tile(p, rr, pair_id, n_pairs, tc, step0, n_steps, valid); ++rr) {
       if (!valid) continue;
@@ -393,9 +394,11 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int cl = limit - key0;                                       // columns > cl are masked
         const int cl_lo = lo_limit - key0;                                 // columns < cl_lo are masked
 
+        long long q0 = prof ? clock64() : 0;
         tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         tmem_ld_wait();
+        if (prof) { r[0] = __float_as_uint(__uint_as_float(r[0]) + 0.f); const long long q1 = clock64(); tph0 += q1 - q0; q0 = q1; }
         if (p.softcap_pre != 0.f) {
           // softcap: s <- tanh(s * scale / softcap); scale_log2 then holds softcap * log2(e)
 #pragma unroll
@@ -415,6 +418,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
 
+        if (prof) { const long long q1 = clock64(); tph1 += q1 - q0; q0 = q1; }
         // combine with the three other threads that hold parts of this row
         float* xs = xchg + (gs & 1) * 256;
         xs[xi] = mx;
@@ -438,6 +442,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           rescale = true;
         }
         const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+        if (prof) { const long long q1 = clock64(); tph2 += q1 - q0; q0 = q1; }
 
         // P = exp2(S * scale_log2 - ms), packed to 16 bit in place (masked entries are -inf -> 0)
 #pragma unroll
@@ -448,6 +453,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           r[i >> 1] = pack2<kFp16>(a, b);
         }
 
+        if (prof) { const long long q1 = clock64(); tph3 += q1 - q0; q0 = q1; }
         // the P buffer and the O accumulators are free once PV of the previous step has completed
         // (for the first step of a tile the epilogue of the previous tile already waited for it)
         if (j > 0) {
@@ -458,6 +464,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (!ok) break;
           tc_fence_after_sync();
         }
+        if (prof) q0 = clock64();
         if (__any_sync(0xffffffffu, rescale)) {
           // this warp group rescales its half of the lane's 256 O columns
 #pragma unroll 1
@@ -479,10 +486,13 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int c = 0; c < 8; ++c)
             st_shared_v4(blk + ((c ^ (row & 7)) << 4), r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
         }
+        long long q2 = prof ? clock64() : 0;
         fence_proxy_async_smem();
+        long long q3 = prof ? clock64() : 0;
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_p_full);
+        if (lane == 0) mbar_arrive_remote(leader_p_full);
+        if (prof) { const long long q4 = clock64(); tph4 += q4 - q0; tph5 += q2 - q0; tph6 += q3 - q2; }
       }
       if (!ok) break;
 
@@ -526,7 +536,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (c2 == 1) {  // O has been read: the next tile's first PV may overwrite it
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_o_free);
+            if (lane == 0) mbar_arrive_remote(leader_o_free);
           }
         }
         uint32_t x[32];
@@ -556,6 +566,13 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       p.debug[100009] = static_cast<float>(t_b);
       p.debug[100010] = static_cast<float>(t_c);
       p.debug[100011] = static_cast<float>(clock64() - t_all);
+      p.debug[100013] = static_cast<float>(tph0);
+      p.debug[100014] = static_cast<float>(tph1);
+      p.debug[100015] = static_cast<float>(tph2);
+      p.debug[100016] = static_cast<float>(tph3);
+      p.debug[100017] = static_cast<float>(tph4);
+      p.debug[100018] = static_cast<float>(tph5);
+      p.debug[100019] = static_cast<float>(tph6);
     }
   }
 

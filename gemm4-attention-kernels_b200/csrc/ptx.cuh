@@ -77,6 +77,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// Same arrive with the default (CTA-scope) release. The cluster-scope release above costs a memory barrier of
+// ~1500 cycles per call (measured in the softmax loop); this form is for the per-step signals whose payload
+// is either nothing in memory (TMEM reads that have completed) or this CTA's own shared memory, made visible
+// to the tensor core by fence.proxy.async before the arrive.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -355,6 +362,15 @@ __device__ __forceinline__ float tanh_approx(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Scheduling fence for values: the compiler must have x[0..n) in registers here and may not move the
+// arithmetic that produces them below this point (used to keep work ahead of a barrier wait).
+template <int kN>
+__device__ __forceinline__ void pin_regs(uint32_t* x) {
+#pragma unroll
+  for (int i = 0; i + 8 <= kN; i += 8)
+    asm volatile("" : "+r"(x[i]), "+r"(x[i + 1]), "+r"(x[i + 2]), "+r"(x[i + 3]), "+r"(x[i + 4]), "+r"(x[i + 5]),
+                      "+r"(x[i + 6]), "+r"(x[i + 7]));
 }
 template <bool kFp16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
