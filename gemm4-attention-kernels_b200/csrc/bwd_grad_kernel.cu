@@ -145,7 +145,7 @@ __device__ __forceinline__ bool grad_decode(const BwdParams& p, const GradLaunch
     const int t_last = min(2 * t.tp + 1, t.n_row_tiles - 1);
     int kv_hi = t.sk;
     if (g.causal) kv_hi = min(kv_hi, min((t_last + 1) * ppp, t.sq) + t.sk - t.sq);
-    t.n_stages = kv_hi > 0 ? ((kv_hi + 255) / 256) * 4 : 0;  // 64-key chunks
+    t.n_stages = kv_hi > 0 ? (kv_hi + 63) / 64 : 0;  // 64-key chunks; dS is zero beyond kv_hi
   }
   return true;
 }

@@ -74,7 +74,7 @@ __device__ __forceinline__ uint32_t slot_set(uint32_t tab, uint32_t s, uint32_t 
 // Tile slot visited by pair `pair` in round r (snake order). Returns false when the slot index is past
 // the end; `valid` says whether the slot holds a tile (the packed layout over-counts slots).
 __device__ __forceinline__ bool fwd_next_tile(const FwdParams& p, int r, int pair, int n_pairs, TileCoord& tc,
-                                              int& step0, int& n_steps, bool& valid) {
+                                              int& step0, int& n_steps, bool& valid, int* last_chunks = nullptr) {
   if (static_cast<long long>(r) * n_pairs >= p.total_pairs) return false;
   const int idx = r * n_pairs + ((r & 1) ? n_pairs - 1 - pair : pair);
   valid = idx < p.total_pairs && decode_tile(p.g, idx, tc);
@@ -91,6 +91,8 @@ __device__ __forceinline__ bool fwd_next_tile(const FwdParams& p, int r, int pai
     if (kv_hi > kv_lo) {
       step0 = kv_lo / fwd::kStepKeys;
       n_steps = (kv_hi + fwd::kStepKeys - 1) / fwd::kStepKeys - step0;
+      // P is zero for every row of the tile beyond kv_hi: the last step's PV only needs this many 64-key chunks
+      if (last_chunks) *last_chunks = (kv_hi - (step0 + n_steps - 1) * fwd::kStepKeys + 63) / 64;
     }
   }
   return true;
@@ -174,10 +176,10 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ++it;
       };
       TileCoord tc;
-      int step0, n_steps;
+      int step0, n_steps, last_chunks = 4;
       bool valid;
       const long long tp0 = prof ? clock64() : 0;
-      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid); ++r) {
+      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid, &last_chunks); ++r) {
         if (!valid || n_steps == 0) continue;
         const int kb = g.cu_k ? 0 : tc.b;
         // Q: two ring acquisitions (4 D blocks of 8 KB each) that stay resident for the whole tile
@@ -207,7 +209,8 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         };
         auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
-          for (int kq = 0; kq < 4 && ok; ++kq) {
+          const int n_kq = j == n_steps - 1 ? last_chunks : 4;
+          for (int kq = 0; kq < n_kq && ok; ++kq) {
             uint32_t st, bar, stage;
             acquire(st, bar, stage);
             if (!ok) break;
@@ -249,7 +252,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = true;
       t_all = prof ? clock64() : 0;
       TileCoord tc;
-      int step0, n_steps;
+      int step0, n_steps, last_chunks = 4;
       bool valid;
       // wait on a barrier with all lanes, keep the outcome warp-uniform
       auto wait_all = [&](uint32_t bar, uint32_t parity, bool cluster_scope) {
@@ -257,7 +260,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                : mbar_wait(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA);
         return __all_sync(0xffffffffu, w);
       };
-      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid); ++r) {
+      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid, &last_chunks); ++r) {
         if (!valid || n_steps == 0) continue;
         // Q of this tile: wait for its two ring entries, hand the previous tile's Q slots to the ring
         uint32_t q_lo[2];
@@ -305,8 +308,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         };
         auto issue_pv = [&](int j) {
+          const int n_kq = j == n_steps - 1 ? last_chunks : 4;
 #pragma unroll 1
-          for (int kq = 0; kq < 4 && ok; ++kq) {
+          for (int kq = 0; kq < n_kq && ok; ++kq) {
             const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
             const long long t0 = prof ? clock64() : 0;
             ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
@@ -324,7 +328,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                              desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
               }
               umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-              if (kq == 3) umma_commit_pair(ctrl + kBarPvDone, 3);
+              if (kq == n_kq - 1) umma_commit_pair(ctrl + kBarPvDone, 3);
             }
             __syncwarp();
             ++it;
