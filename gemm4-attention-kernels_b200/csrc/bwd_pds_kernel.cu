@@ -37,7 +37,8 @@ constexpr int kBarFullV = kBarEmptyK + 8 * kStages;
 constexpr int kBarEmptyV = kBarFullV + 8 * kStages;
 constexpr int kBarSdpFull = kBarEmptyV + 8 * kStages;  // [2], two arrivals each: the S issuer's and the dP issuer's commit
 constexpr int kBarSdpFree = kBarSdpFull + 16;          // [2], leader CTA only
-constexpr int kTmemPtr = kBarSdpFree + 16;
+constexpr int kBarDoFull = kBarSdpFree + 16;
+constexpr int kTmemPtr = kBarDoFull + 8;
 constexpr int kAbort = kTmemPtr + 4;
 constexpr int kCtrlBytes = 256;
 constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
@@ -84,6 +85,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(ctrl + kBarQFull, 1);
+    mbar_init(ctrl + kBarDoFull, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(ctrl + kBarFullK + 8 * s, 1);
       mbar_init(ctrl + kBarEmptyK + 8 * s, 1);
@@ -113,13 +115,16 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0 && n_steps > 0) {
-      if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarQFull, 4 * 65536);
+      // Q and dO signal separate barriers: the QK^T issuer starts as soon as Q has landed
+      const uint32_t leader_do_full = mapa_u32(ctrl + kBarDoFull, 0);
+      if (rank == 0) {
+        mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * 65536);
+        mbar_arrive_expect_tx(ctrl + kBarDoFull, 2 * 65536);
+      }
       const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
       const int qb = g.cu_q ? 0 : tc.b;
-      for (int d = 0; d < 8; ++d) {
-        tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
-        tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
-      }
+      for (int d = 0; d < 8; ++d) tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+      for (int d = 0; d < 8; ++d) tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_do_full, d * 64, 0, qpos, tc.hu, qb);
       const int kb = g.cu_k ? 0 : tc.b;
       const uint32_t leader_full_k = mapa_u32(ctrl + kBarFullK, 0), leader_full_v = mapa_u32(ctrl + kBarFullV, 0);
       uint32_t it = 0;
@@ -155,7 +160,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const bool prof_t = prof && is_s;
       uint32_t it = 0;
       t_all = prof_t ? clock64() : 0;
-      bool ok = mbar_wait(ctrl + kBarQFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      bool ok = mbar_wait(ctrl + (is_s ? kBarQFull : kBarDoFull), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
       for (int j = 0; j < n_steps && ok; ++j) {
