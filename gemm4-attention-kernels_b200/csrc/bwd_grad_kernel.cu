@@ -203,21 +203,23 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp runs the loop, one elected lane issues the copies (the warp-uniform form spends about
+    // half the cycles per stage of a single lane under a divergent branch).
+    {
       bool ok = true;
       uint32_t it = 0;
       const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0);
-      auto acquire = [&](uint32_t& st, uint32_t& bar) {
+      auto acquire = [&](uint32_t& st, uint32_t& bar, uint32_t& stage) {
         const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
         ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
-        if (!ok) return;
-        if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+        ok = __all_sync(0xffffffffu, ok);
         bar = leader_full0 + 8 * s;
         st = sRing + s * kStageBytes;
+        stage = s;
         ++it;
       };
       for (int n = 0; ok; ++n) {
-        const int idx = tq_fetch(tq, n, false, abort_flag, p.status);
+        const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
         if (idx < 0 || idx >= total_tiles) break;
         if (!grad_decode(p, gl, idx, t) || t.n_stages == 0) continue;
         if (t.mode != kModeDQ) {
@@ -230,19 +232,23 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
             // walking down from the common end keeps the pairs that run side by side on the same Q / dO rows
             for (int rt = t.n_row_tiles - 1; rt >= t.t_min && ok; --rt) {
               for (int c = 0; c < 2 && ok; ++c) {
-                uint32_t st = 0, bar = 0;
-                acquire(st, bar);
+                uint32_t st = 0, bar = 0, stage = 0;
+                acquire(st, bar, stage);
                 if (!ok) break;
                 const int ws_row = (t.tile_base + rt) * kRowsPerPair + c * kRowsPerCta;
-                tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, h * 2 + t.mode);
-                tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, h * 2 + t.mode);
                 const int pos = t.q_off + rt * ppp + c * g.pos_per_cta;
+                if (elect_one()) {
+                  if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+                  tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, h * 2 + t.mode);
+                  tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, h * 2 + t.mode);
 #pragma unroll
-                for (int m = 0; m < 2; ++m) {
-                  const int d0 = m * 256 + rank * 128;
-                  tma_load_5d_pair(st + 16384 + m * 16384, tm_b, bar, d0, 0, pos, h, qb);
-                  tma_load_5d_pair(st + 16384 + m * 16384 + 8192, tm_b, bar, d0 + 64, 0, pos, h, qb);
+                  for (int m = 0; m < 2; ++m) {
+                    const int d0 = m * 256 + rank * 128;
+                    tma_load_5d_pair(st + 16384 + m * 16384, tm_b, bar, d0, 0, pos, h, qb);
+                    tma_load_5d_pair(st + 16384 + m * 16384 + 8192, tm_b, bar, d0 + 64, 0, pos, h, qb);
+                  }
                 }
+                __syncwarp();
               }
             }
           }
@@ -251,17 +257,21 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
           const int my_tile_ld = min(2 * t.tp + rank, t.n_row_tiles - 1);  // clamped when the last pair has one tile
           const int ws_row = (t.tile_base + my_tile_ld) * kRowsPerPair;
           for (int c = 0; c < t.n_stages && ok; ++c) {
-            uint32_t st = 0, bar = 0;
-            acquire(st, bar);
+            uint32_t st = 0, bar = 0, stage = 0;
+            acquire(st, bar, stage);
             if (!ok) break;
-            tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, t.hu * 2 + 1);
-            tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, t.hu * 2 + 1);
+            if (elect_one()) {
+              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+              tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, t.hu * 2 + 1);
+              tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, t.hu * 2 + 1);
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-              const int d0 = m * 256 + rank * 128;
-              tma_load_4d_pair(st + 16384 + m * 16384, &tm_k, bar, d0, t.k_off + c * 64, t.kvh, kb);
-              tma_load_4d_pair(st + 16384 + m * 16384 + 8192, &tm_k, bar, d0 + 64, t.k_off + c * 64, t.kvh, kb);
+              for (int m = 0; m < 2; ++m) {
+                const int d0 = m * 256 + rank * 128;
+                tma_load_4d_pair(st + 16384 + m * 16384, &tm_k, bar, d0, t.k_off + c * 64, t.kvh, kb);
+                tma_load_4d_pair(st + 16384 + m * 16384 + 8192, &tm_k, bar, d0 + 64, t.k_off + c * 64, t.kvh, kb);
+              }
             }
+            __syncwarp();
           }
         }
       }

@@ -114,17 +114,23 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t leader_q_full = mapa_u32(ctrl + kBarQFull, 0);
 
   if (warp == 0) {
-    if (lane == 0 && n_steps > 0) {
-      // Q and dO signal separate barriers: the QK^T issuer starts as soon as Q has landed
+    // TMA producer: the whole warp runs the loop, one elected lane issues (same reason as for the MMA issuers
+    // below: the warp-uniform form spends about half the cycles per stage, and a busy producer is latency
+    // added to every freed ring slot).
+    if (n_steps > 0) {
       const uint32_t leader_do_full = mapa_u32(ctrl + kBarDoFull, 0);
-      if (rank == 0) {
-        mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * 65536);
-        mbar_arrive_expect_tx(ctrl + kBarDoFull, 2 * 65536);
-      }
       const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
       const int qb = g.cu_q ? 0 : tc.b;
-      for (int d = 0; d < 8; ++d) tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
-      for (int d = 0; d < 8; ++d) tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_do_full, d * 64, 0, qpos, tc.hu, qb);
+      if (elect_one()) {
+        // Q and dO signal separate barriers: the QK^T issuer starts as soon as Q has landed
+        if (rank == 0) {
+          mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * 65536);
+          mbar_arrive_expect_tx(ctrl + kBarDoFull, 2 * 65536);
+        }
+        for (int d = 0; d < 8; ++d) tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+        for (int d = 0; d < 8; ++d) tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_do_full, d * 64, 0, qpos, tc.hu, qb);
+      }
+      __syncwarp();
       const int kb = g.cu_k ? 0 : tc.b;
       const uint32_t leader_full_k = mapa_u32(ctrl + kBarFullK, 0), leader_full_v = mapa_u32(ctrl + kBarFullV, 0);
       uint32_t it = 0;
@@ -134,13 +140,21 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int c = 0; c < 8 && ok; ++c) {  // K and V boxes alternate so that both issuers are fed evenly
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           ok = mbar_wait(ctrl + kBarEmptyK + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullK + 8 * s, 2 * kStageBytes);
-          tma_load_4d_pair(sRingK + s * kStageBytes, &tm_k, leader_full_k + 8 * s, c * 64, key0, tc.hkv, kb);
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullK + 8 * s, 2 * kStageBytes);
+            tma_load_4d_pair(sRingK + s * kStageBytes, &tm_k, leader_full_k + 8 * s, c * 64, key0, tc.hkv, kb);
+          }
+          __syncwarp();
           ok = mbar_wait(ctrl + kBarEmptyV + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullV + 8 * s, 2 * kStageBytes);
-          tma_load_4d_pair(sRingV + s * kStageBytes, &tm_v, leader_full_v + 8 * s, c * 64, key0, tc.hkv, kb);
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullV + 8 * s, 2 * kStageBytes);
+            tma_load_4d_pair(sRingV + s * kStageBytes, &tm_v, leader_full_v + 8 * s, c * 64, key0, tc.hkv, kb);
+          }
+          __syncwarp();
           ++it;
         }
       }

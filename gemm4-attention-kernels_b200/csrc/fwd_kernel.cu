@@ -158,18 +158,24 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // Like the MMA issuer below, the whole warp runs the loop and one elected lane issues the copies: the
+    // warp-uniform form spends about half the cycles per stage of a single lane under a divergent branch,
+    // and every cycle this warp is busy is a cycle a freed ring slot waits for its next load.
+    {
       uint32_t it = 0;      // ring acquisitions so far (Q takes two per tile)
       bool ok = true;
       uint32_t rs = 0x3210u;  // logical ring stage -> physical slot (one nibble each)
       uint32_t qs = 0x54u;    // slots that held the previous tile's Q (free at the start)
       const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0);
+      // wait for the stage's slot with all lanes (warp-uniform outcome); the elected lane arms the barrier
       auto acquire = [&](uint32_t& st, uint32_t& bar, uint32_t& stage) {
         const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
         const long long t0 = prof ? clock64() : 0;
-        ok = ok && mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+        if (ok) {
+          ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          ok = __all_sync(0xffffffffu, ok);
+        }
         if (prof) t_a += clock64() - t0;
-        if (ok && rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
         st = sSlots + slot_get(rs, s) * kStageBytes;
         bar = leader_full0 + 8 * s;
         stage = s;
@@ -191,8 +197,13 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint32_t st, bar, stage;
             acquire(st, bar, stage);
             if (!ok) break;
-            for (int d = 0; d < 4; ++d)
-              tma_load_5d_pair(st + d * 8192, &tm_q, bar, (u * 4 + d) * 64, 0, qpos, tc.hu, qb);
+            if (elect_one()) {
+              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+#pragma unroll
+              for (int d = 0; d < 4; ++d)
+                tma_load_5d_pair(st + d * 8192, &tm_q, bar, (u * 4 + d) * 64, 0, qpos, tc.hu, qb);
+            }
+            __syncwarp();
             newq = slot_set(newq, u, slot_get(rs, stage));
             rs = slot_set(rs, stage, slot_get(qs, u));  // the previous tile's Q slot joins the ring here
           }
@@ -204,8 +215,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint32_t st, bar, stage;
             acquire(st, bar, stage);
             if (!ok) break;
-            tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
-            tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
+            if (elect_one()) {
+              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+              tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
+              tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
+            }
+            __syncwarp();
           }
         };
         auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
@@ -215,12 +230,16 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             acquire(st, bar, stage);
             if (!ok) break;
             const int key0 = tc.k_off + (step0 + j) * kStepKeys + kq * 64;
+            if (elect_one()) {
+              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-              const int dv0 = m * 256 + static_cast<int>(rank) * 128;
-              tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
-              tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+              for (int m = 0; m < 2; ++m) {
+                const int dv0 = m * 256 + static_cast<int>(rank) * 128;
+                tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
+                tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
+              }
             }
+            __syncwarp();
           }
         };
         load_k(0);
@@ -229,7 +248,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           load_v(j);
         }
       }
-      if (prof) {
+      if (prof && lane == 0) {
         p.debug[100000] = static_cast<float>(t_a);
         p.debug[100001] = static_cast<float>(clock64() - tp0);
       }
