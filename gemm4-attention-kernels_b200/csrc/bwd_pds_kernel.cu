@@ -5,11 +5,14 @@
 // (bwd_grad_kernel.cu) and nothing is recomputed. The reference recomputes S and dP in each of four
 // D passes of both of its backward kernels (3.8x the useful FLOPs).
 //
-// Query-stationary CTA pair, cta_group::2 UMMAs with M = 128 (64 packed rows per CTA), N = 256 keys per
-// step. No accumulator lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns:
-// the tensor pipe fills one pair while eight element-wise warps drain the other. Q and dO (64 x 512 each)
-// stay in shared memory; K rows and V rows stream through two rings of 3 x 16 KB, one per issuing thread
-// (two independent issue streams and finer stages keep more of the K/V stream in flight).
+// CTA pair, cta_group::2 UMMAs with M = 128 (64 packed rows per CTA), N = 256 keys per step. No accumulator
+// lives across steps, so TMEM holds two (S, dP) buffer pairs of 128 + 128 columns: the tensor pipe fills one
+// pair while eight element-wise warps drain the other.
+// What bounds this kernel is the operand stream: a load takes ~1700 cycles from issue to landing, so the
+// bytes per cycle it delivers are (ring bytes in flight) / 1700, and with Q and dO both resident (128 KB) only
+// 96 KB of ring were left for 256 KB of K/V per step. Hence only dO (64 x 512) stays resident; the Q tile is
+// re-streamed with the K rows (an 8 KB Q block rides in every K stage, +25 % L2 traffic), which buys rings of
+// 4 x 24 KB (K rows + Q block) for the QK^T issuer and 4 x 16 KB (V rows) for the dO V^T issuer.
 // A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
 // the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
 // fully masked and therefore zero.
@@ -23,15 +26,16 @@ namespace sd {
 
 namespace pds {
 constexpr int kStepKeys = 256;
-constexpr int kStages = 3;            // per ring; one ring for K rows, one for V rows
-constexpr int kStageBytes = 16384;    // one TMA box: this CTA's 128 keys x 64 of the 512 D columns
-constexpr int kOffQ = 0;
-constexpr int kOffDO = 65536;
-constexpr int kOffRingK = 131072;
-constexpr int kOffRingV = kOffRingK + kStages * kStageBytes;
-constexpr int kOffCtrl = kOffRingV + kStages * kStageBytes;
-constexpr int kBarQFull = 0;
-constexpr int kBarFullK = 8;
+constexpr int kStages = 4;            // per ring; one ring for K rows (+ Q block), one for V rows
+constexpr int kBoxBytes = 16384;      // one K / V TMA box: this CTA's 128 keys x 64 of the 512 D columns
+constexpr int kQBoxBytes = 8192;      // the tile's 64 rows x the same 64 D columns of Q
+constexpr int kStageK = kBoxBytes + kQBoxBytes;
+constexpr int kStageV = kBoxBytes;
+constexpr int kOffDO = 0;
+constexpr int kOffRingK = 65536;
+constexpr int kOffRingV = kOffRingK + kStages * kStageK;
+constexpr int kOffCtrl = kOffRingV + kStages * kStageV;
+constexpr int kBarFullK = 0;
 constexpr int kBarEmptyK = kBarFullK + 8 * kStages;
 constexpr int kBarFullV = kBarEmptyK + 8 * kStages;
 constexpr int kBarEmptyV = kBarFullV + 8 * kStages;
@@ -42,6 +46,8 @@ constexpr int kTmemPtr = kBarDoFull + 8;
 constexpr int kAbort = kTmemPtr + 4;
 constexpr int kCtrlBytes = 256;
 constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
+static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(kAbort + 4 <= kCtrlBytes, "control block overflow");
 }  // namespace pds
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
@@ -56,7 +62,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_SMEM_ALIGN);
     return;
   }
-  const uint32_t sQ = smem_base + kOffQ, sDO = smem_base + kOffDO;
+  const uint32_t sDO = smem_base + kOffDO;
   const uint32_t sRingK = smem_base + kOffRingK, sRingV = smem_base + kOffRingV, ctrl = smem_base + kOffCtrl;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
@@ -84,7 +90,6 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(ctrl + kBarQFull, 1);
     mbar_init(ctrl + kBarDoFull, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(ctrl + kBarFullK + 8 * s, 1);
@@ -111,7 +116,6 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  const uint32_t leader_q_full = mapa_u32(ctrl + kBarQFull, 0);
 
   if (warp == 0) {
     // TMA producer: the whole warp runs the loop, one elected lane issues (same reason as for the MMA issuers
@@ -122,12 +126,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
       const int qb = g.cu_q ? 0 : tc.b;
       if (elect_one()) {
-        // Q and dO signal separate barriers: the QK^T issuer starts as soon as Q has landed
-        if (rank == 0) {
-          mbar_arrive_expect_tx(ctrl + kBarQFull, 2 * 65536);
-          mbar_arrive_expect_tx(ctrl + kBarDoFull, 2 * 65536);
-        }
-        for (int d = 0; d < 8; ++d) tma_load_5d_pair(sQ + d * 8192, &tm_q, leader_q_full, d * 64, 0, qpos, tc.hu, qb);
+        if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarDoFull, 2 * 65536);
         for (int d = 0; d < 8; ++d) tma_load_5d_pair(sDO + d * 8192, &tm_do, leader_do_full, d * 64, 0, qpos, tc.hu, qb);
       }
       __syncwarp();
@@ -143,16 +142,17 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullK + 8 * s, 2 * kStageBytes);
-            tma_load_4d_pair(sRingK + s * kStageBytes, &tm_k, leader_full_k + 8 * s, c * 64, key0, tc.hkv, kb);
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullK + 8 * s, 2 * kStageK);
+            tma_load_4d_pair(sRingK + s * kStageK, &tm_k, leader_full_k + 8 * s, c * 64, key0, tc.hkv, kb);
+            tma_load_5d_pair(sRingK + s * kStageK + kBoxBytes, &tm_q, leader_full_k + 8 * s, c * 64, 0, qpos, tc.hu, qb);
           }
           __syncwarp();
           ok = mbar_wait(ctrl + kBarEmptyV + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullV + 8 * s, 2 * kStageBytes);
-            tma_load_4d_pair(sRingV + s * kStageBytes, &tm_v, leader_full_v + 8 * s, c * 64, key0, tc.hkv, kb);
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFullV + 8 * s, 2 * kStageV);
+            tma_load_4d_pair(sRingV + s * kStageV, &tm_v, leader_full_v + 8 * s, c * 64, key0, tc.hkv, kb);
           }
           __syncwarp();
           ++it;
@@ -168,13 +168,14 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (rank == 0 && n_steps > 0) {
       const bool is_s = warp == 1;
       constexpr uint32_t idesc = make_idesc(false, false, false, 128, kStepKeys);
-      const uint32_t a_lo = desc_lo(is_s ? sQ : sDO, 16), ring_lo = desc_lo(is_s ? sRingK : sRingV, 16);
+      const uint32_t do_lo = desc_lo(sDO, 16), ring_lo = desc_lo(is_s ? sRingK : sRingV, 16);
+      const uint32_t stage16 = (is_s ? kStageK : kStageV) >> 4;
       const uint32_t bar_full = ctrl + (is_s ? kBarFullK : kBarFullV), bar_empty = ctrl + (is_s ? kBarEmptyK : kBarEmptyV);
       const uint32_t d_off = is_s ? 0 : 128;
       const bool prof_t = prof && is_s;
       uint32_t it = 0;
       t_all = prof_t ? clock64() : 0;
-      bool ok = mbar_wait(ctrl + (is_s ? kBarQFull : kBarDoFull), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
+      bool ok = is_s ? true : mbar_wait(ctrl + kBarDoFull, 0, abort_flag, p.status, ST_TIMEOUT_MMA);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after_sync();
       for (int j = 0; j < n_steps && ok; ++j) {
@@ -197,8 +198,9 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (prof_t) t_a += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t a0 = a_lo + c * (8192 >> 4);
-          const uint32_t b0 = ring_lo + s * (kStageBytes >> 4);
+          const uint32_t b0 = ring_lo + s * stage16;
+          // A: the Q block that came with this K stage / the resident dO block of the same 64 D columns
+          const uint32_t a0 = is_s ? b0 + (kBoxBytes >> 4) : do_lo + c * (8192 >> 4);
           if (elect_one()) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
