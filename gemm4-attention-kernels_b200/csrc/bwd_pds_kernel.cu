@@ -262,11 +262,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_ld_wait();
       // P (fp32, kept in s[]); masked entries are forced to zero (warp-uniform fast path without masks)
       const bool full = __all_sync(0xffffffffu, cl >= 63);
-#ifdef PDS_NO_MATH
-      if (false) {
-#else
       if (full) {
-#endif
 #pragma unroll
         for (int i = 0; i < 64; ++i) s[i] = __float_as_uint(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2)));
       } else {
@@ -319,12 +315,7 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int r = 0; r < 4; ++r) {
         // this thread now holds chunk (lane & 3) of row (lane & ~3) + r; its own row is `lane`
         const int64_t row_delta = static_cast<int64_t>((lane & ~3) + r - lane) * p.ws_pitch;
-#ifdef PDS_STORE_LOCAL
-        // experiment: same store instructions, but every CTA keeps hitting one small L2-resident region
-        uint16_t* dst_p = p.ws + (static_cast<int64_t>(blockIdx.x) * 64 + ((lane & ~3) + r + q * 32 & 63)) * p.ws_pitch + (key0 & 255) + (lane & 3) * 16;
-#else
         uint16_t* dst_p = ws_p + row_delta + key0 + (lane & 3) * 16;
-#endif
         st_global_v8(dst_p, &pk[8 * r]);
         st_global_v8(dst_p + plane, &dk[8 * r]);
       }

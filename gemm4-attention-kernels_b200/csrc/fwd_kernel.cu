@@ -121,7 +121,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const TileGeom& g = p.g;
 
-  // optional per-role cycle counters of pair 0 (tests / tuning only)
+  // optional per-role cycle counters of pair 0 (tests / tuning only), written to debug[32..51]
   const bool prof = p.debug != nullptr && pair_id == 0 && rank == 0;
   long long t_a = 0, t_b = 0, t_c = 0, t_all = 0;
 
@@ -249,8 +249,8 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       if (prof && lane == 0) {
-        p.debug[100000] = static_cast<float>(t_a);
-        p.debug[100001] = static_cast<float>(clock64() - tp0);
+        p.debug[32] = static_cast<float>(t_a);
+        p.debug[33] = static_cast<float>(clock64() - tp0);
       }
     }
   } else if (warp == 1) {
@@ -370,11 +370,11 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ++tiles;
       }
       if (prof && lane == 0) {
-        p.debug[100002] = static_cast<float>(gs);
-        p.debug[100004] = static_cast<float>(t_a);
-        p.debug[100005] = static_cast<float>(t_b);
-        p.debug[100006] = static_cast<float>(t_c);
-        p.debug[100007] = static_cast<float>(clock64() - t_all);
+        p.debug[34] = static_cast<float>(gs);
+        p.debug[36] = static_cast<float>(t_a);
+        p.debug[37] = static_cast<float>(t_b);
+        p.debug[38] = static_cast<float>(t_c);
+        p.debug[39] = static_cast<float>(clock64() - t_all);
       }
     }
   } else if (warp >= 4) {
@@ -585,17 +585,17 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
     if (prof && warp == 4 && lane == 0) {
-      p.debug[100008] = static_cast<float>(t_a);
-      p.debug[100009] = static_cast<float>(t_b);
-      p.debug[100010] = static_cast<float>(t_c);
-      p.debug[100011] = static_cast<float>(clock64() - t_all);
-      p.debug[100013] = static_cast<float>(tph0);
-      p.debug[100014] = static_cast<float>(tph1);
-      p.debug[100015] = static_cast<float>(tph2);
-      p.debug[100016] = static_cast<float>(tph3);
-      p.debug[100017] = static_cast<float>(tph4);
-      p.debug[100018] = static_cast<float>(tph5);
-      p.debug[100019] = static_cast<float>(tph6);
+      p.debug[40] = static_cast<float>(t_a);
+      p.debug[41] = static_cast<float>(t_b);
+      p.debug[42] = static_cast<float>(t_c);
+      p.debug[43] = static_cast<float>(clock64() - t_all);
+      p.debug[45] = static_cast<float>(tph0);
+      p.debug[46] = static_cast<float>(tph1);
+      p.debug[47] = static_cast<float>(tph2);
+      p.debug[48] = static_cast<float>(tph3);
+      p.debug[49] = static_cast<float>(tph4);
+      p.debug[50] = static_cast<float>(tph5);
+      p.debug[51] = static_cast<float>(tph6);
     }
   }
 

@@ -82,7 +82,8 @@ typedef struct {
   /* device word; a kernel that gives up a bounded wait stores a positive code here (0 = fine). */
   int32_t* status_flag; /* may be NULL */
 
-  /* optional fp32 device buffer receiving per-role cycle counters of one CTA pair (tests / tuning only) */
+  /* optional fp32 device buffer of at least 64 elements receiving per-role cycle counters of one CTA pair
+     (tests / tuning only): [0,8) P/dS kernel, [8,16) gradient kernel, [32,52) forward kernel */
   float* debug;
 
   /* ---- forward-only score modifiers (the backward rejects them, like src/interface.py:676-683) ---- */
