@@ -121,3 +121,58 @@ def test_c_abi_rejects_missing_workspace():
     lib = _capi.load_library()
     assert lib.splitd_bwd_workspace_bytes(ctypes.byref(p)) == 2 * 2 * 128 * (256 + 64) * 2 + 256  # tiles + work counters
     assert lib.splitd_bwd_dq(ctypes.byref(p), None) == -5
+
+
+def test_debug_counters_stay_inside_64_floats():
+    """The optional `debug` buffer of the C-ABI is documented as 64 floats (include/splitd_attn.h): the
+    kernels' cycle counters must land there and nowhere behind it, and results must not change."""
+    from splitd_flash_attn import interface as I
+
+    torch.manual_seed(5)
+    q, k, v, do = _t(1, 1024, 8, D), _t(1, 1024, 1, D), _t(1, 1024, 1, D), _t(1, 1024, 8, D)
+    out0, lse0 = I._flash_attn_fwd(q, k, v, causal=True, return_lse=True)
+    g0 = I._flash_attn_bwd(q, k, v, out0, do, lse0, causal=True)
+    buf = torch.zeros(256, device="cuda")
+    out1, lse1 = I._flash_attn_fwd(q, k, v, causal=True, return_lse=True, debug=buf)
+    g1 = I._flash_attn_bwd(q, k, v, out1, do, lse1, causal=True, debug=buf)
+    torch.cuda.synchronize()
+    assert I.kernel_status() == 0
+    assert torch.count_nonzero(buf[64:]) == 0
+    assert torch.count_nonzero(buf[32:52]) > 0 and torch.count_nonzero(buf[:16]) > 0
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+    for a, b in zip(g0, g1):
+        assert torch.equal(a, b)
+
+
+def test_two_streams_side_by_side():
+    """Calls on different streams share nothing but the library: each backward has its own workspace (and with
+    it its own work counter), so overlapping launches must give the same bits as running alone."""
+    from splitd_flash_attn import split_flash_attn_func
+
+    torch.manual_seed(6)
+    cases = []
+    for S in (512, 768):
+        q, k, v = (_t(2, S, 8, D).requires_grad_(True), _t(2, S, 2, D).requires_grad_(True),
+                   _t(2, S, 2, D).requires_grad_(True))
+        cases.append((q, k, v, _t(2, S, 8, D)))
+
+    def run(q, k, v, do):
+        out = split_flash_attn_func(q, k, v, causal=True)
+        return (out.detach(),) + torch.autograd.grad(out, (q, k, v), do)
+
+    alone = [run(*c) for c in cases]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in cases]
+    together = []
+    for _ in range(3):  # a few rounds so that the launches really interleave
+        together = []
+        for c, st in zip(cases, streams):
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                together.append(run(*c))
+    for st in streams:
+        torch.cuda.current_stream().wait_stream(st)
+    torch.cuda.synchronize()
+    for a, b in zip(alone, together):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
