@@ -16,7 +16,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "libsplitd_attn.so")
-SOURCES = ["capi.cu", "fwd_kernel.cu", "bwd_preprocess.cu", "bwd_pds_kernel.cu", "bwd_grad_kernel.cu", "no_alloc.cu"]
+SOURCES = ["capi.cu", "fwd_kernel.cu", "bwd_preprocess.cu", "bwd_pds_kernel.cu",
+    "bwd_pds2_kernel.cu", "bwd_grad_kernel.cu", "no_alloc.cu"]
 
 
 def _nvcc() -> str:

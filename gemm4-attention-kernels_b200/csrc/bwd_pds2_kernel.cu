@@ -1,0 +1,459 @@
+// Backward step 2a, two-pass form: the P tiles and the dS tiles are produced by two launches of one kernel.
+//     pass 0:  S  = Q K^T      ->  P  = exp2(S*scale*log2e - lse_log2)          (written to the workspace)
+//     pass 1:  dP = dO V^T     ->  dS = P * (dP - dpsum) * scale                (P read back, dS written)
+// (the math of src/fmha_dq_sm90_d512.py:1040-1090 / src/fmha_dkdv_sm90_d512.py:1060-1130 of the reference).
+//
+// Why two passes: with ONE resident A operand (Q or dO) a CTA can hold 128 rows of it (128 KB), so every MMA
+// is a cta_group::2 UMMA with M = 256 (128 rows per CTA, TMEM lane = row), N = 256 keys: 128 cycles per
+// MMA for 4 KB of streamed B operand per CTA instead of 64 cycles, i.e. half the K/V bytes per FLOP of the
+// one-pass kernel (bwd_pds_kernel.cu), whose speed is set by that stream. The price is 2 bytes per (row, key)
+// of extra HBM traffic (pass 1 reads P).
+//
+// CTA pair = two 128-row tiles (even, odd) of one (batch, head unit); CTA c owns tile 2*tp + c. The pair
+// runs over the key range of its odd tile (the later one under a causal mask); blocks that are masked for
+// the even tile come out as zeros, which is what the gradient GEMMs expect.
+// Shared memory: A resident (128 x 512 bf16 = 128 KB, reloaded per tile in eight 64-column blocks, each as
+// soon as the previous tile's last step has used it), B ring 6 x 16 KB. TMEM: two 256-column buffers.
+// Persistent pairs drawing tiles from a work counter (tile_queue.cuh); whole-warp issue loops with an elected
+// lane (see bwd_pds_kernel.cu for the measurements behind both).
+#include <cstring>
+
+#include "common.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
+#include "tile_queue.cuh"
+
+namespace sd {
+
+namespace pds2 {
+constexpr int kStepKeys = 256;
+constexpr int kStages = 6;
+constexpr int kStageBytes = 16384;   // this CTA's 128 keys x 64 of the 512 D columns
+constexpr int kABlockBytes = 16384;  // the tile's 128 rows x the same 64 D columns
+constexpr int kOffA = 0;
+constexpr int kOffRing = 8 * kABlockBytes;
+constexpr int kOffCtrl = kOffRing + kStages * kStageBytes;
+constexpr int kBarFull = 0;
+constexpr int kBarEmpty = kBarFull + 8 * kStages;
+constexpr int kBarAFull = kBarEmpty + 8 * kStages;  // [8] one per 64-column block of A
+constexpr int kBarAFree = kBarAFull + 64;           // [8]
+constexpr int kBarOutFull = kBarAFree + 64;         // [2]
+constexpr int kBarOutFree = kBarOutFull + 16;       // [2], leader CTA only
+constexpr int kTmemPtr = kBarOutFree + 16;
+constexpr int kAbort = kTmemPtr + 4;
+constexpr int kTileQ = kAbort + 4;
+constexpr int kCtrlBytes = 320;
+constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
+constexpr int kThreads = 384;
+constexpr int kConsumers = 2 + 1 + 16;  // producers of both CTAs, the MMA issuer, element-wise warps of both CTAs
+static_assert(kTileQ % 8 == 0 && kTileQ + kTileQueueBytes <= kCtrlBytes, "control block overflow");
+static_assert(kSmemBytes <= 232448, "shared memory budget");
+}  // namespace pds2
+
+struct PairTile {
+  int b, hu, hkv, tp;
+  int sq, sk, q_off, k_off;
+  int tile_base, n_row_tiles;
+  int n_steps;
+};
+
+// Tile pair `idx` of the launch (heaviest first under a causal mask). `ppu`: tile pairs per head unit
+// (packed layout: an upper bound over all sequences; batched: per sequence).
+__device__ __forceinline__ bool pds2_decode(const BwdParams& p, int ppu, int idx, PairTile& t) {
+  const TileGeom& g = p.g;
+  const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
+  t.q_off = 0, t.k_off = 0;
+  if (g.cu_q == nullptr) {
+    t.tp = idx % ppu;
+    idx /= ppu;
+    t.b = idx % g.batch;
+    t.hu = idx / g.batch;
+    t.sq = g.seqlen_q, t.sk = g.seqlen_k;
+    t.n_row_tiles = g.row_tiles;
+    t.tile_base = t.b * g.row_tiles;
+    if (g.causal) t.tp = ppu - 1 - t.tp;
+  } else {
+    t.hu = idx / ppu;
+    const int r = idx - t.hu * ppu;
+    int acc_p = 0, acc_r = 0;
+    t.b = -1;
+    for (int i = 0; i < g.batch; ++i) {
+      const int q0 = g.cu_q[i], q1 = g.cu_q[i + 1];
+      const int nrt = (q1 - q0 + ppp - 1) / ppp, np = (nrt + 1) / 2;
+      if (r < acc_p + np) {
+        t.b = i, t.tp = r - acc_p, t.sq = q1 - q0, t.q_off = q0, t.n_row_tiles = nrt;
+        t.k_off = g.cu_k[i];
+        t.sk = g.cu_k[i + 1] - t.k_off;
+        if (g.causal) t.tp = np - 1 - t.tp;
+        break;
+      }
+      acc_p += np;
+      acc_r += nrt;
+    }
+    if (t.b < 0) return false;
+    t.tile_base = acc_r;
+  }
+  if (t.hu >= g.head_units) return false;
+  t.hkv = (g.pack_g == g.group) ? t.hu : t.hu / g.group;
+  const int t_last = min(2 * t.tp + 1, t.n_row_tiles - 1);
+  int kv_hi = t.sk;
+  if (g.causal) kv_hi = min(kv_hi, min((t_last + 1) * ppp, t.sq) + t.sk - t.sq);
+  t.n_steps = kv_hi > 0 ? (kv_hi + pds2::kStepKeys - 1) / pds2::kStepKeys : 0;
+  return true;
+}
+
+__device__ __forceinline__ void ld_global_v8(const void* p, uint32_t* w) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p)
+               : "memory");
+}
+
+template <int kMode>  // 0: S -> P, 1: dP -> dS
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pds2::kThreads, 1)
+splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                       const BwdParams p, const int total_tiles, const int ppu) {
+  using namespace pds2;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw;
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_SMEM_ALIGN);
+    return;
+  }
+  const uint32_t sA = smem_base + kOffA, sRing = smem_base + kOffRing, ctrl = smem_base + kOffCtrl;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffCtrl + kAbort);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kOffCtrl + kTmemPtr);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const TileGeom& g = p.g;
+  const int ppp = 2 * g.pos_per_cta;
+
+  // optional cycle counters of one pair: debug[0..5] pass 0, debug[16..21] pass 1
+  const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
+  float* dbg = p.debug + (kMode ? 16 : 0);
+  long long t_a = 0, t_b = 0, t_c = 0;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(ctrl + kBarFull + 8 * s, 1);
+      mbar_init(ctrl + kBarEmpty + 8 * s, 1);
+    }
+    for (int c = 0; c < 8; ++c) {
+      mbar_init(ctrl + kBarAFull + 8 * c, 1);
+      mbar_init(ctrl + kBarAFree + 8 * c, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(ctrl + kBarOutFull + 8 * b, 1);
+      mbar_init(ctrl + kBarOutFree + 8 * b, 16);  // 8 element-wise warps x 2 CTAs
+    }
+    tq_init(ctrl + kTileQ, kConsumers);
+    fence_mbar_init();
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(ctrl + kTmemPtr, 512);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const TileQueue tq = tq_make(ctrl + kTileQ);
+  PairTile t;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (whole warp, elected lane)
+    const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0), leader_a_full0 = mapa_u32(ctrl + kBarAFull, 0);
+    uint32_t it = 0, tiles = 0;
+    bool ok = true;
+    for (int n = 0; ok; ++n) {
+      const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
+      if (idx < 0 || idx >= total_tiles) break;
+      if (!pds2_decode(p, ppu, idx, t) || t.n_steps == 0) continue;
+      const int rt_ld = min(2 * t.tp + rank, t.n_row_tiles - 1);  // clamped when the last pair has one tile
+      const int apos = t.q_off + rt_ld * ppp;
+      const int qb = g.cu_q ? 0 : t.b, kb = g.cu_k ? 0 : t.b;
+      for (int j = 0; j < t.n_steps && ok; ++j) {
+        const int key0 = t.k_off + j * kStepKeys + rank * 128;
+        for (int c = 0; c < 8 && ok; ++c) {
+          if (j == 0) {
+            // block c of this tile's A operand, as soon as the previous tile's last step has read the old one
+            if (tiles > 0) {
+              ok = mbar_wait(ctrl + kBarAFree + 8 * c, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_LOAD);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+            }
+            if (elect_one()) {
+              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarAFull + 8 * c, 2 * kABlockBytes);
+              tma_load_5d_pair(sA + c * kABlockBytes, &tm_a, leader_a_full0 + 8 * c, c * 64, 0, apos, t.hu, qb);
+            }
+            __syncwarp();
+          }
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+            tma_load_4d_pair(sRing + s * kStageBytes, &tm_b, leader_full0 + 8 * s, c * 64, key0, t.hkv, kb);
+          }
+          __syncwarp();
+          ++it;
+        }
+      }
+      ++tiles;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA, whole warp)
+    if (rank == 0) {
+      constexpr uint32_t idesc = make_idesc(false, false, false, 256, kStepKeys);
+      const uint32_t a_lo = desc_lo(sA, 16), ring_lo = desc_lo(sRing, 16);
+      uint32_t it = 0, gs = 0, tiles = 0;
+      bool ok = true;
+      const long long t_begin = prof ? clock64() : 0;
+      for (int n = 0; ok; ++n) {
+        const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
+        if (idx < 0 || idx >= total_tiles) break;
+        if (!pds2_decode(p, ppu, idx, t) || t.n_steps == 0) continue;
+        for (int j = 0; j < t.n_steps && ok; ++j, ++gs) {
+          const uint32_t b = gs & 1;
+          if (gs >= 2) {  // buffer b must have been drained
+            const long long t0 = prof ? clock64() : 0;
+            ok = mbar_wait<true>(ctrl + kBarOutFree + 8 * b, ((gs >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = __all_sync(0xffffffffu, ok);
+            if (prof) t_b += clock64() - t0;
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          const uint32_t d_tmem = tmem_base + b * 256;
+          const bool last_step = j == t.n_steps - 1;
+#pragma unroll 1
+          for (int c = 0; c < 8 && ok; ++c) {
+            const long long t0 = prof ? clock64() : 0;
+            if (j == 0) {  // this tile's block c of A has landed
+              ok = mbar_wait(ctrl + kBarAFull + 8 * c, tiles & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+            }
+            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+            ok = __all_sync(0xffffffffu, ok);
+            if (prof) t_a += clock64() - t0;
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t a0 = a_lo + c * (kABlockBytes >> 4), b0 = ring_lo + s * (kStageBytes >> 4);
+            if (elect_one()) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
+              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+              if (last_step) umma_commit_pair(ctrl + kBarAFree + 8 * c, 3);  // block c of A may be overwritten
+              if (c == 7) umma_commit_pair(ctrl + kBarOutFull + 8 * b, 3);
+            }
+            __syncwarp();
+            ++it;
+          }
+        }
+        ++tiles;
+      }
+      if (prof && lane == 0) {
+        dbg[0] = static_cast<float>(t_a);
+        dbg[1] = static_cast<float>(t_b);
+        dbg[2] = static_cast<float>(clock64() - t_begin);
+        dbg[3] = static_cast<float>(gs);
+      }
+    }
+  } else if (warp == 3) {
+    if (rank == 0 && lane == 0)
+      tq_schedule(ctrl + kTileQ, p.tile_counters + (kMode ? kCounterPds2 : kCounterPds), pair_id, n_pairs, total_tiles,
+                  abort_flag, p.status);
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ element-wise warps
+    // TMEM lane = row of the tile; warp & 3 selects the 32 lanes, (warp - 4) / 4 the 128-key half of the step.
+    const int q = warp & 3, ch = (warp - 4) >> 2;
+    const int L = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int64_t plane = p.ws_rows * p.ws_pitch;
+    const uint32_t leader_free0 = mapa_u32(ctrl + kBarOutFree, 0);
+    bool ok = true;
+    uint32_t gs = 0;
+    const long long t_begin = prof ? clock64() : 0;
+    for (int n = 0; ok; ++n) {
+      const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
+      if (idx < 0 || idx >= total_tiles) break;
+      if (!pds2_decode(p, ppu, idx, t) || t.n_steps == 0) continue;
+      const int rt = 2 * t.tp + rank;
+      const bool tile_valid = rt < t.n_row_tiles;  // the last pair of a sequence may hold one tile only
+      const int pos = rt * ppp + L / g.pack_g;
+      const int head = (g.pack_g > 1) ? t.hu * g.pack_g + L % g.pack_g : t.hu;
+      const bool row_ok = tile_valid && pos < t.sq;
+      int limit = t.sk - 1;
+      if (g.causal) limit = min(limit, pos + t.sk - t.sq);
+      if (!row_ok) limit = -1;
+      float stat = 0.f;  // pass 0: lse_log2 of the row; pass 1: -dpsum * scale
+      if (row_ok) {
+        const int64_t ridx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + t.q_off + pos
+                                    : (static_cast<int64_t>(t.b) * g.heads_q + head) * t.sq + pos;
+        stat = kMode == 0 ? p.lse_log2[ridx] : -p.dpsum[ridx] * p.scale;
+      }
+      // this thread's row in the P plane; the dS plane is `plane` elements further
+      uint16_t* ws_row = p.ws + (static_cast<int64_t>(t.hu) * 2) * plane +
+                         (static_cast<int64_t>(t.tile_base + min(rt, t.n_row_tiles - 1)) * kRowsPerPair + L) * p.ws_pitch;
+      // after the 4 x 4 chunk transposes a thread handles chunk (lane & 3) of rows (lane & ~3) + r, r = 0..3
+      const int64_t row_delta0 = static_cast<int64_t>((lane & ~3) - lane) * p.ws_pitch;
+
+      // pass 1: the P values of this thread's 128 keys of a step, two per word: plain 32-byte loads of the
+      // thread's own row (whole sectors, so nothing is fetched twice; only the stores need the chunk transposes).
+      // Each 64-key half is re-loaded for the NEXT step as soon as this step is done with it, so the latency
+      // of the loads hides behind the rest of the step.
+      uint32_t pq[64];
+      auto load_p_half = [&](int step, int h2) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          if (tile_valid)
+            ld_global_v8(ws_row + step * kStepKeys + ch * 128 + h2 * 64 + r * 16, &pq[h2 * 32 + 8 * r]);
+          else
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pq[h2 * 32 + 8 * r + i] = 0u;
+        }
+      };
+      if (kMode == 1) {
+        load_p_half(0, 0);
+        load_p_half(0, 1);
+      }
+      for (int j = 0; j < t.n_steps && ok; ++j, ++gs) {
+        const uint32_t b = gs & 1;
+        const int key_base = j * kStepKeys + ch * 128;
+        const long long t0 = prof ? clock64() : 0;
+        ok = mbar_wait(ctrl + kBarOutFull + 8 * b, (gs >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+        if (prof) t_c += clock64() - t0;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          uint32_t s[64];
+          const uint32_t addr = lane_addr + b * 256 + ch * 128 + h2 * 64;
+          tmem_ld32(addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+          tmem_ld32(addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+          tmem_ld_wait();
+          if (h2 == 1) {  // the buffer has been read: hand it back to the tensor pipe
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_free0 + 8 * b);
+          }
+          const int key0 = key_base + h2 * 64;
+          const int cl = limit - key0;  // columns > cl are masked
+          uint32_t x[32];
+          const bool full = __all_sync(0xffffffffu, cl >= 63);  // warp-uniform fast path without masks
+          if (kMode == 0) {
+            if (full) {
+#pragma unroll
+              for (int i = 0; i < 64; i += 2)
+                x[i >> 1] = pack2<false>(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -stat)),
+                                         ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -stat)));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 64; i += 2) {
+                const float a = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -stat));
+                const float bb = ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -stat));
+                x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+              }
+            }
+          } else {
+            const uint32_t* pw = &pq[h2 * 32];
+            if (full) {
+#pragma unroll
+              for (int i = 0; i < 64; i += 2) {
+                const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
+                x[i >> 1] = pack2<false>(p0 * fmaf(__uint_as_float(s[i]), p.scale, stat),
+                                         p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, stat));
+              }
+            } else {
+              // P is already 0 where masked; the select only guards against non-finite dP of rows / keys
+              // outside the sequence
+#pragma unroll
+              for (int i = 0; i < 64; i += 2) {
+                const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
+                const float a = p0 * fmaf(__uint_as_float(s[i]), p.scale, stat);
+                const float bb = p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, stat);
+                x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+              }
+            }
+            if (j + 1 < t.n_steps) load_p_half(j + 1, h2);  // these registers are free again: next step's P
+          }
+          // 64 keys x 2 bytes = 4 chunks of 32 bytes per row; after the transpose every 256-bit store
+          // instruction of the warp writes whole 128-byte lines
+          transpose_chunks32_4x4(x, lane);
+          if (tile_valid) {
+            uint16_t* dst = ws_row + (kMode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) st_global_v8(dst + r * p.ws_pitch, &x[8 * r]);
+          }
+        }
+      }
+    }
+    if (prof && warp == 4 && lane == 0) {
+      dbg[4] = static_cast<float>(t_c);
+      dbg[5] = static_cast<float>(clock64() - t_begin);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<2>(tmem_base, 512);
+  }
+}
+
+template <int kMode>
+static int launch_pass(const splitd_params* p, const BwdParams& bp, cudaStream_t stream) {
+  const TileGeom& g = bp.g;
+  CUtensorMap tm_a, tm_b;
+  if (kMode == 0) {
+    if (int e = make_q_tmap(&tm_a, p->q, p, g, p->q_strides, 2 * g.pos_per_cta, "q")) return e;
+    if (int e = make_kv_tmap(&tm_b, p->k, p, p->k_strides, 128, "k")) return e;
+  } else {
+    if (int e = make_q_tmap(&tm_a, p->dout, p, g, p->do_strides, 2 * g.pos_per_cta, "dout")) return e;
+    if (int e = make_kv_tmap(&tm_b, p->v, p, p->v_strides, 128, "v")) return e;
+  }
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  const int ppu = varlen ? (g.row_tiles + g.batch + 1) / 2 : (g.row_tiles + 1) / 2;
+  const long long pairs = static_cast<long long>(ppu) * g.head_units * (varlen ? 1 : g.batch);
+  if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "P/dS grid out of range");
+  auto kern = splitd_bwd_pds2_kernel<kMode>;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pds2::kSmemBytes);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(pds2): %s", cudaGetErrorString(ce));
+  static int cache[64] = {};
+  const int resident = resident_cluster_pairs(kern, pds2::kThreads, pds2::kSmemBytes, cache);
+  const long long grid_pairs = pairs < resident ? pairs : resident;
+  ce = cudaMemsetAsync(bp.tile_counters + (kMode ? kCounterPds2 : kCounterPds), 0, sizeof(int), stream);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
+  kern<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(pds2::kThreads), pds2::kSmemBytes, stream>>>(
+      tm_a, tm_b, bp, static_cast<int>(pairs), ppu);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "P/dS launch failed: %s", cudaGetErrorString(ce));
+  return 0;
+}
+
+int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream) {
+  BwdParams bp;
+  if (int e = fill_bwd_params(p, bp)) return e;
+  if (int e = check_workspace(p)) return e;
+  if (int e = launch_pass<0>(p, bp, stream)) return e;
+  return launch_pass<1>(p, bp, stream);
+}
+
+}  // namespace sd

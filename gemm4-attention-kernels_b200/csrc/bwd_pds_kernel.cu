@@ -19,6 +19,7 @@
 // A tile pair (even tile, odd tile) always writes the same number of 256-key blocks (the odd tile's), so
 // the dQ GEMM can run both tiles of a pair over one key range; the surplus block of the even tile is
 // fully masked and therefore zero.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -402,6 +403,11 @@ splitd_bwd_pds_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 }
 
 int launch_bwd_pds(const splitd_params* p, cudaStream_t stream) {
+  // Default: the two-pass form (bwd_pds2_kernel.cu). SPLITD_PDS_ONE_PASS=1 in the environment selects the
+  // one-pass kernel below, which moves 2 bytes per (row, key) less through HBM but streams K/V at twice the
+  // bytes per FLOP; it is read once per process.
+  static const int one_pass = [] { const char* e = getenv("SPLITD_PDS_ONE_PASS"); return e && e[0] == '1'; }();
+  if (!one_pass) return launch_bwd_pds_two_pass(p, stream);
   BwdParams bp;
   if (int e = fill_bwd_params(p, bp)) return e;
   if (int e = check_workspace(p)) return e;

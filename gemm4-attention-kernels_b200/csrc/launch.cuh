@@ -22,6 +22,7 @@ int make_kv_tmap(CUtensorMap* map, const void* base, const splitd_params* p, con
 int launch_fwd(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_preprocess(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_pds(const splitd_params* p, cudaStream_t stream);
+int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_grad(const splitd_params* p, cudaStream_t stream, int modes);
 int launch_bwd_dq(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_dkdv(const splitd_params* p, cudaStream_t stream);

@@ -73,7 +73,19 @@ def main():
 
     run("cuBLAS bf16 8192^3", lambda: torch.matmul(a, b), 2.0 * 8192 ** 3)
     run("forward", lambda: I._flash_attn_fwd(q, k, v, causal=False, return_lse=True), F)
-    run("backward (pre+tiles+grads)", lambda: I._flash_attn_bwd(q, k, v, out, do, lse, causal=False), 2.5 * F)
+    stages = []
+
+    def bwd():
+        evs = []
+        I._flash_attn_bwd(q, k, v, out, do, lse, causal=False, stage_events=evs)
+        stages.append(evs)
+
+    run("backward (pre+tiles+grads)", bwd, 2.5 * F)
+    torch.cuda.synchronize()
+    half = stages[len(stages) // 2:]
+    t = [sum(e[i].elapsed_time(e[i + 1]) for e in half) / len(half) for i in range(3)]
+    print(f"  inside it: preprocess {t[0]:.3f} ms | P/dS tiles {t[1]:.3f} ms ({F / t[1] / 1e9:.0f} TFLOP/s) | "
+          f"dQ+dK+dV GEMMs {t[2]:.3f} ms ({1.5 * F / t[2] / 1e9:.0f} TFLOP/s)")
     print("status", I.kernel_status())
 
 
