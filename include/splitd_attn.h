@@ -127,10 +127,12 @@ int splitd_bwd_dq(const splitd_params* p, void* stream);
  * the same stream with the same params. */
 int splitd_bwd_dkdv(const splitd_params* p, void* stream);
 
-/* The two launches splitd_bwd is made of after the preprocess step, for callers that want to time or
- * schedule them separately (no counterpart in the reference, whose kernels recompute instead):
+/* The two steps splitd_bwd is made of after the preprocess step, for callers that want to time or schedule
+ * them separately (no counterpart in the reference, whose kernels recompute instead):
  * splitd_bwd_tiles writes the bf16 P and dS tiles to `workspace` (S = QK^T and dP = dO V^T on the tensor
- * cores); splitd_bwd_grads computes dq, dk and dv from them in one launch. */
+ * cores; two launches, P first; SPLITD_PDS_ONE_PASS=1 in the environment selects a single-launch form that
+ * moves less through HBM and is a little slower); splitd_bwd_grads computes dq, dk and dv from them in one
+ * launch. */
 int splitd_bwd_tiles(const splitd_params* p, void* stream);
 int splitd_bwd_grads(const splitd_params* p, void* stream);
 

@@ -102,3 +102,40 @@ def test_config1_against_reference_golden():
     assert np.abs(sub(dq) - g["dq"]).max() < 5e-2
     assert np.abs(sub(dk) - g["dk"]).max() < 1e-1
     assert np.abs(sub(dv) - g["dv"]).max() < 1e-1
+
+
+def test_one_pass_tile_kernel_agrees_with_default():
+    """SPLITD_PDS_ONE_PASS=1 (read once per process, hence the child process) selects the single-launch P/dS
+    kernel; its gradients must agree with the default two-pass path to bf16 rounding."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+
+    code = r'''
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from splitd_flash_attn import interface as I
+torch.manual_seed(11)
+B, S, HQ, HKV, D = 2, 640, 8, 2, 512
+q = torch.randn(B, S, HQ, D, device="cuda", dtype=torch.bfloat16)
+k = torch.randn(B, S, HKV, D, device="cuda", dtype=torch.bfloat16)
+v = torch.randn(B, S, HKV, D, device="cuda", dtype=torch.bfloat16)
+do = torch.randn(B, S, HQ, D, device="cuda", dtype=torch.bfloat16)
+out, lse = I._flash_attn_fwd(q, k, v, causal=True, return_lse=True)
+g = I._flash_attn_bwd(q, k, v, out, do, lse, causal=True)
+torch.cuda.synchronize()
+assert I.kernel_status() == 0
+torch.save([t.float().cpu() for t in g], sys.argv[2])
+'''
+    pkg = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gemm4-attention-kernels_b200")
+    res = []
+    with tempfile.TemporaryDirectory() as tmp:
+        for one_pass in ("0", "1"):
+            path = os.path.join(tmp, f"g{one_pass}.pt")
+            env = dict(os.environ, SPLITD_PDS_ONE_PASS=one_pass)
+            subprocess.run([sys.executable, "-c", code, pkg, path], check=True, env=env, timeout=300)
+            res.append(torch.load(path))
+    for a, b in zip(*res):
+        scale = a.abs().max().item()
+        assert (a - b).abs().max().item() <= 2e-2 * scale  # both are bf16 results of the same fp32 quantities
