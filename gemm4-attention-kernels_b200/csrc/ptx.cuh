@@ -363,15 +363,6 @@ __device__ __forceinline__ float tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// Scheduling fence for values: the compiler must have x[0..n) in registers here and may not move the
-// arithmetic that produces them below this point (used to keep work ahead of a barrier wait).
-template <int kN>
-__device__ __forceinline__ void pin_regs(uint32_t* x) {
-#pragma unroll
-  for (int i = 0; i + 8 <= kN; i += 8)
-    asm volatile("" : "+r"(x[i]), "+r"(x[i + 1]), "+r"(x[i + 2]), "+r"(x[i + 3]), "+r"(x[i + 4]), "+r"(x[i + 5]),
-                      "+r"(x[i + 6]), "+r"(x[i + 7]));
-}
 template <bool kFp16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (kFp16) {
