@@ -200,7 +200,7 @@ def run_ours(args):
             out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True)
             evs = []
             I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs)
-            launches += 5  # forward, preprocess, P pass, dS pass, gradient GEMMs
+            launches += 4  # forward, preprocess, P/dS tiles, gradient GEMMs
             if record is not None:
                 record.append(((B, S, causal), [e0] + evs))
         return launches
@@ -242,8 +242,7 @@ def run_ours(args):
     bwd_tflops = 2.5 * total_fwd * n_steps / (kt["bwd_preprocess"] + kt["bwd_tiles"] + kt["bwd_grads"]) / 1e9
 
     # ---- roofline of the dominant kernel (tensor bound). Algorithmic FLOPs per launch, with F = forward FLOPs:
-    #      forward kernel F; P/dS tile kernels F (S and dP GEMMs, two launches timed together); gradient GEMM
-    #      kernel 1.5 F (dQ, dK, dV).
+    #      forward kernel F; P/dS tile kernel F (S and dP GEMMs); gradient GEMM kernel 1.5 F (dQ, dK, dV).
     #      DRAM traffic per launch: ncu capture at B=1,S=4096 non-causal (profiles/), scaled by FLOPs -- the
     #      workspace traffic of both backward kernels grows with rows*keys, i.e. in proportion to the FLOPs.
     peak, peak_sus, peak_kind = load_peaks()
@@ -254,7 +253,7 @@ def run_ours(args):
     fwd_dram_bytes_per_launch = 0.274e9 * (16384 / 4096)
     dom = max(algo, key=lambda n: kt[n])
     achieved = algo[dom] * n_steps / kt[dom] / 1e9
-    n_launch = len(cases)  # per-launch figures of bwd_tiles cover its two launches (P pass + dS pass) together
+    n_launch = len(cases)
     traffic = fwd_dram_bytes_per_launch if dom == "fwd" else dram_bytes_per_flop[dom] * algo[dom] / n_launch
     # The kernels are timed back to back inside a step of ~0.2 s that runs under the power cap, so the
     # denominator is the sustained cuBLAS figure; the burst figure (a kernel timed alone) is given beside it.

@@ -1,4 +1,4 @@
-// Backward step 2a, two-pass form: the P tiles and the dS tiles are produced by two launches of one kernel.
+// Backward step 2a, two-pass form: P and dS come from two GEMM passes that alternate inside one kernel.
 //     pass 0:  S  = Q K^T      ->  P  = exp2(S*scale*log2e - lse_log2)          (written to the workspace)
 //     pass 1:  dP = dO V^T     ->  dS = P * (dP - dpsum) * scale                (P read back, dS written)
 // (the math of src/fmha_dq_sm90_d512.py:1040-1090 / src/fmha_dkdv_sm90_d512.py:1060-1130 of the reference).
@@ -6,16 +6,18 @@
 // Why two passes: with ONE resident A operand (Q or dO) a CTA can hold 128 rows of it (128 KB), so every MMA
 // is a cta_group::2 UMMA with M = 256 (128 rows per CTA, TMEM lane = row), N = 256 keys: 128 cycles per
 // MMA for 4 KB of streamed B operand per CTA instead of 64 cycles, i.e. half the K/V bytes per FLOP of the
-// one-pass kernel (bwd_pds_kernel.cu), whose speed is set by that stream. The price is 2 bytes per (row, key)
-// of extra HBM traffic (pass 1 reads P).
+// one-pass kernel (bwd_pds_kernel.cu), whose speed is set by that stream.
+// Why they alternate: a pair runs pass 0 over a chunk of kChunkSteps key steps and then pass 1 over the same
+// chunk, so the P values pass 1 reads (<= 1 MB per pair) are still in L2 and HBM sees each tile element twice
+// (P out, dS out) like in the one-pass kernel. The resident operand is swapped at every pass switch, block by
+// block as the previous pass's last step releases it.
 //
 // CTA pair = two 128-row tiles (even, odd) of one (batch, head unit); CTA c owns tile 2*tp + c. The pair
 // runs over the key range of its odd tile (the later one under a causal mask); blocks that are masked for
 // the even tile come out as zeros, which is what the gradient GEMMs expect.
-// Shared memory: A resident (128 x 512 bf16 = 128 KB, reloaded per tile in eight 64-column blocks, each as
-// soon as the previous tile's last step has used it), B ring 6 x 16 KB. TMEM: two 256-column buffers.
-// Persistent pairs drawing tiles from a work counter (tile_queue.cuh); whole-warp issue loops with an elected
-// lane (see bwd_pds_kernel.cu for the measurements behind both).
+// Shared memory: A resident (128 x 512 bf16 = 128 KB in eight 64-column blocks), B ring 6 x 16 KB. TMEM: two
+// 256-column buffers. Persistent pairs drawing tiles from a work counter (tile_queue.cuh); whole-warp issue
+// loops with an elected lane (see bwd_pds_kernel.cu for the measurements behind both).
 #include <cstring>
 
 #include "common.cuh"
@@ -27,6 +29,7 @@ namespace sd {
 
 namespace pds2 {
 constexpr int kStepKeys = 256;
+constexpr int kChunkSteps = 8;       // key steps per pass before the pair switches to the other pass
 constexpr int kStages = 6;
 constexpr int kStageBytes = 16384;   // this CTA's 128 keys x 64 of the 512 D columns
 constexpr int kABlockBytes = 16384;  // the tile's 128 rows x the same 64 D columns
@@ -109,9 +112,9 @@ __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t* w) {
                : "memory");
 }
 
-template <int kMode>  // 0: S -> P, 1: dP -> dS
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pds2::kThreads, 1)
-splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                        const BwdParams p, const int total_tiles, const int ppu) {
   using namespace pds2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -131,9 +134,9 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;
 
-  // optional cycle counters of one pair: debug[0..5] pass 0, debug[16..21] pass 1
+  // optional cycle counters of one pair (debug[0..5]), summed over its tiles
   const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
-  float* dbg = p.debug + (kMode ? 16 : 0);
+  float* dbg = p.debug;
   long long t_a = 0, t_b = 0, t_c = 0;
 
   if (threadIdx.x == 0) {
@@ -152,8 +155,10 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     }
     tq_init(ctrl + kTileQ, kConsumers);
     fence_mbar_init();
-    prefetch_tmap(&tm_a);
-    prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
   }
   if (warp == 1) {
     tmem_alloc<2>(ctrl + kTmemPtr, 512);
@@ -170,7 +175,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (whole warp, elected lane)
     const uint32_t leader_full0 = mapa_u32(ctrl + kBarFull, 0), leader_a_full0 = mapa_u32(ctrl + kBarAFull, 0);
-    uint32_t it = 0, tiles = 0;
+    uint32_t it = 0, segs = 0;  // ring stages issued / (chunk, pass) segments started, over all tiles
     bool ok = true;
     for (int n = 0; ok; ++n) {
       const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
@@ -179,88 +184,99 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       const int rt_ld = min(2 * t.tp + rank, t.n_row_tiles - 1);  // clamped when the last pair has one tile
       const int apos = t.q_off + rt_ld * ppp;
       const int qb = g.cu_q ? 0 : t.b, kb = g.cu_k ? 0 : t.b;
-      for (int j = 0; j < t.n_steps && ok; ++j) {
-        const int key0 = t.k_off + j * kStepKeys + rank * 128;
-        for (int c = 0; c < 8 && ok; ++c) {
-          if (j == 0) {
-            // block c of this tile's A operand, as soon as the previous tile's last step has read the old one
-            if (tiles > 0) {
-              ok = mbar_wait(ctrl + kBarAFree + 8 * c, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_LOAD);
+      for (int c0 = 0; c0 < t.n_steps && ok; c0 += kChunkSteps) {
+        const int c1 = min(c0 + kChunkSteps, t.n_steps);
+        for (int mode = 0; mode < 2 && ok; ++mode, ++segs) {
+          const CUtensorMap* tm_a = mode ? &tm_do : &tm_q;
+          const CUtensorMap* tm_b = mode ? &tm_v : &tm_k;
+          for (int j = c0; j < c1 && ok; ++j) {
+            const int key0 = t.k_off + j * kStepKeys + rank * 128;
+            for (int c = 0; c < 8 && ok; ++c) {
+              if (j == c0) {
+                // block c of this segment's A operand, as soon as the previous segment's last step has read
+                // the old one
+                if (segs > 0) {
+                  ok = mbar_wait(ctrl + kBarAFree + 8 * c, (segs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_LOAD);
+                  ok = __all_sync(0xffffffffu, ok);
+                  if (!ok) break;
+                }
+                if (elect_one()) {
+                  if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarAFull + 8 * c, 2 * kABlockBytes);
+                  tma_load_5d_pair(sA + c * kABlockBytes, tm_a, leader_a_full0 + 8 * c, c * 64, 0, apos, t.hu, qb);
+                }
+                __syncwarp();
+              }
+              const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+              ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) break;
+              if (elect_one()) {
+                if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
+                tma_load_4d_pair(sRing + s * kStageBytes, tm_b, leader_full0 + 8 * s, c * 64, key0, t.hkv, kb);
+              }
+              __syncwarp();
+              ++it;
             }
-            if (elect_one()) {
-              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarAFull + 8 * c, 2 * kABlockBytes);
-              tma_load_5d_pair(sA + c * kABlockBytes, &tm_a, leader_a_full0 + 8 * c, c * 64, 0, apos, t.hu, qb);
-            }
-            __syncwarp();
           }
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          ok = mbar_wait(ctrl + kBarEmpty + 8 * s, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_LOAD);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * s, 2 * kStageBytes);
-            tma_load_4d_pair(sRing + s * kStageBytes, &tm_b, leader_full0 + 8 * s, c * 64, key0, t.hkv, kb);
-          }
-          __syncwarp();
-          ++it;
         }
       }
-      ++tiles;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA, whole warp)
     if (rank == 0) {
       constexpr uint32_t idesc = make_idesc(false, false, false, 256, kStepKeys);
       const uint32_t a_lo = desc_lo(sA, 16), ring_lo = desc_lo(sRing, 16);
-      uint32_t it = 0, gs = 0, tiles = 0;
+      uint32_t it = 0, gs = 0, segs = 0;
       bool ok = true;
       const long long t_begin = prof ? clock64() : 0;
       for (int n = 0; ok; ++n) {
         const int idx = tq_fetch(tq, n, true, abort_flag, p.status);
         if (idx < 0 || idx >= total_tiles) break;
         if (!pds2_decode(p, ppu, idx, t) || t.n_steps == 0) continue;
-        for (int j = 0; j < t.n_steps && ok; ++j, ++gs) {
-          const uint32_t b = gs & 1;
-          if (gs >= 2) {  // buffer b must have been drained
-            const long long t0 = prof ? clock64() : 0;
-            ok = mbar_wait<true>(ctrl + kBarOutFree + 8 * b, ((gs >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
-            ok = __all_sync(0xffffffffu, ok);
-            if (prof) t_b += clock64() - t0;
-            if (!ok) break;
-            tc_fence_after_sync();
-          }
-          const uint32_t d_tmem = tmem_base + b * 256;
-          const bool last_step = j == t.n_steps - 1;
+        for (int c0 = 0; c0 < t.n_steps && ok; c0 += kChunkSteps) {
+          const int c1 = min(c0 + kChunkSteps, t.n_steps);
+          for (int mode = 0; mode < 2 && ok; ++mode, ++segs) {
+            for (int j = c0; j < c1 && ok; ++j, ++gs) {
+              const uint32_t b = gs & 1;
+              if (gs >= 2) {  // buffer b must have been drained
+                const long long t0 = prof ? clock64() : 0;
+                ok = mbar_wait<true>(ctrl + kBarOutFree + 8 * b, ((gs >> 1) - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+                ok = __all_sync(0xffffffffu, ok);
+                if (prof) t_b += clock64() - t0;
+                if (!ok) break;
+                tc_fence_after_sync();
+              }
+              const uint32_t d_tmem = tmem_base + b * 256;
+              const bool last_step = j == c1 - 1;
 #pragma unroll 1
-          for (int c = 0; c < 8 && ok; ++c) {
-            const long long t0 = prof ? clock64() : 0;
-            if (j == 0) {  // this tile's block c of A has landed
-              ok = mbar_wait(ctrl + kBarAFull + 8 * c, tiles & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
-              ok = __all_sync(0xffffffffu, ok);
-              if (!ok) break;
-            }
-            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-            ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
-            ok = __all_sync(0xffffffffu, ok);
-            if (prof) t_a += clock64() - t0;
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t a0 = a_lo + c * (kABlockBytes >> 4), b0 = ring_lo + s * (kStageBytes >> 4);
-            if (elect_one()) {
+              for (int c = 0; c < 8 && ok; ++c) {
+                const long long t0 = prof ? clock64() : 0;
+                if (j == c0) {  // this segment's block c of A has landed
+                  ok = mbar_wait(ctrl + kBarAFull + 8 * c, segs & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+                  ok = __all_sync(0xffffffffu, ok);
+                  if (!ok) break;
+                }
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                ok = mbar_wait(ctrl + kBarFull + 8 * s, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
+                ok = __all_sync(0xffffffffu, ok);
+                if (prof) t_a += clock64() - t0;
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t a0 = a_lo + c * (kABlockBytes >> 4), b0 = ring_lo + s * (kStageBytes >> 4);
+                if (elect_one()) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
-              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-              if (last_step) umma_commit_pair(ctrl + kBarAFree + 8 * c, 3);  // block c of A may be overwritten
-              if (c == 7) umma_commit_pair(ctrl + kBarOutFull + 8 * b, 3);
+                  for (int k = 0; k < 4; ++k)
+                    umma_ss<2>(d_tmem, desc_join(a0 + ((k * 32) >> 4)), desc_join(b0 + ((k * 32) >> 4)), idesc, (c | k) != 0);
+                  umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+                  if (last_step) umma_commit_pair(ctrl + kBarAFree + 8 * c, 3);  // block c of A may be overwritten
+                  if (c == 7) umma_commit_pair(ctrl + kBarOutFull + 8 * b, 3);
+                }
+                __syncwarp();
+                ++it;
+              }
             }
-            __syncwarp();
-            ++it;
           }
         }
-        ++tiles;
       }
       if (prof && lane == 0) {
         dbg[0] = static_cast<float>(t_a);
@@ -271,8 +287,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     }
   } else if (warp == 3) {
     if (rank == 0 && lane == 0)
-      tq_schedule(ctrl + kTileQ, p.tile_counters + (kMode ? kCounterPds2 : kCounterPds), pair_id, n_pairs, total_tiles,
-                  abort_flag, p.status);
+      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterPds, pair_id, n_pairs, total_tiles, abort_flag, p.status);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ element-wise warps
     // TMEM lane = row of the tile; warp & 3 selects the 32 lanes, (warp - 4) / 4 the 128-key half of the step.
@@ -296,11 +311,12 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       int limit = t.sk - 1;
       if (g.causal) limit = min(limit, pos + t.sk - t.sq);
       if (!row_ok) limit = -1;
-      float stat = 0.f;  // pass 0: lse_log2 of the row; pass 1: -dpsum * scale
+      float lse2 = 0.f, nds = 0.f;  // lse_log2 of the row (pass 0); -dpsum * scale (pass 1)
       if (row_ok) {
         const int64_t ridx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + t.q_off + pos
                                     : (static_cast<int64_t>(t.b) * g.heads_q + head) * t.sq + pos;
-        stat = kMode == 0 ? p.lse_log2[ridx] : -p.dpsum[ridx] * p.scale;
+        lse2 = p.lse_log2[ridx];
+        nds = -p.dpsum[ridx] * p.scale;
       }
       // this thread's row in the P plane; the dS plane is `plane` elements further
       uint16_t* ws_row = p.ws + (static_cast<int64_t>(t.hu) * 2) * plane +
@@ -309,7 +325,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
       const int64_t row_delta0 = static_cast<int64_t>((lane & ~3) - lane) * p.ws_pitch;
 
       // pass 1: the P values of this thread's 128 keys of a step, two per word: plain 32-byte loads of the
-      // thread's own row (whole sectors, so nothing is fetched twice; only the stores need the chunk transposes).
+      // thread's own row (whole sectors; only the stores need the chunk transposes). The values were stored by
+      // lanes of this same warp a chunk of steps ago (__syncwarp orders the two) and normally still sit in L2.
       // Each 64-key half is re-loaded for the NEXT step as soon as this step is done with it, so the latency
       // of the loads hides behind the rest of the step.
       uint32_t pq[64];
@@ -323,78 +340,84 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
             for (int i = 0; i < 8; ++i) pq[h2 * 32 + 8 * r + i] = 0u;
         }
       };
-      if (kMode == 1) {
-        load_p_half(0, 0);
-        load_p_half(0, 1);
-      }
-      for (int j = 0; j < t.n_steps && ok; ++j, ++gs) {
-        const uint32_t b = gs & 1;
-        const int key_base = j * kStepKeys + ch * 128;
-        const long long t0 = prof ? clock64() : 0;
-        ok = mbar_wait(ctrl + kBarOutFull + 8 * b, (gs >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-        if (prof) t_c += clock64() - t0;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          uint32_t s[64];
-          const uint32_t addr = lane_addr + b * 256 + ch * 128 + h2 * 64;
-          tmem_ld32(addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-          tmem_ld32(addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-          tmem_ld_wait();
-          if (h2 == 1) {  // the buffer has been read: hand it back to the tensor pipe
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(leader_free0 + 8 * b);
+      for (int c0 = 0; c0 < t.n_steps && ok; c0 += kChunkSteps) {
+        const int c1 = min(c0 + kChunkSteps, t.n_steps);
+        for (int mode = 0; mode < 2 && ok; ++mode) {
+          if (mode == 1) {
+            __syncwarp();  // the P stores of this chunk (other lanes of this warp) before the loads below
+            load_p_half(c0, 0);
+            load_p_half(c0, 1);
           }
-          const int key0 = key_base + h2 * 64;
-          const int cl = limit - key0;  // columns > cl are masked
-          uint32_t x[32];
-          const bool full = __all_sync(0xffffffffu, cl >= 63);  // warp-uniform fast path without masks
-          if (kMode == 0) {
-            if (full) {
+          for (int j = c0; j < c1 && ok; ++j, ++gs) {
+            const uint32_t b = gs & 1;
+            const int key_base = j * kStepKeys + ch * 128;
+            const long long t0 = prof ? clock64() : 0;
+            ok = mbar_wait(ctrl + kBarOutFull + 8 * b, (gs >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+            if (prof) t_c += clock64() - t0;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
 #pragma unroll
-              for (int i = 0; i < 64; i += 2)
-                x[i >> 1] = pack2<false>(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -stat)),
-                                         ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -stat)));
-            } else {
+            for (int h2 = 0; h2 < 2; ++h2) {
+              uint32_t s[64];
+              const uint32_t addr = lane_addr + b * 256 + ch * 128 + h2 * 64;
+              tmem_ld32(addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+              tmem_ld32(addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+              tmem_ld_wait();
+              if (h2 == 1) {  // the buffer has been read: hand it back to the tensor pipe
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(leader_free0 + 8 * b);
+              }
+              const int key0 = key_base + h2 * 64;
+              const int cl = limit - key0;  // columns > cl are masked
+              uint32_t x[32];
+              const bool full = __all_sync(0xffffffffu, cl >= 63);  // warp-uniform fast path without masks
+              if (mode == 0) {
+                if (full) {
 #pragma unroll
-              for (int i = 0; i < 64; i += 2) {
-                const float a = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -stat));
-                const float bb = ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -stat));
-                x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+                  for (int i = 0; i < 64; i += 2)
+                    x[i >> 1] = pack2<false>(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2)),
+                                             ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2)));
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 64; i += 2) {
+                    const float a = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
+                    const float bb = ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2));
+                    x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+                  }
+                }
+              } else {
+                const uint32_t* pw = &pq[h2 * 32];
+                if (full) {
+#pragma unroll
+                  for (int i = 0; i < 64; i += 2) {
+                    const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
+                    x[i >> 1] = pack2<false>(p0 * fmaf(__uint_as_float(s[i]), p.scale, nds),
+                                             p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, nds));
+                  }
+                } else {
+                  // P is already 0 where masked; the select only guards against non-finite dP of rows / keys
+                  // outside the sequence
+#pragma unroll
+                  for (int i = 0; i < 64; i += 2) {
+                    const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
+                    const float a = p0 * fmaf(__uint_as_float(s[i]), p.scale, nds);
+                    const float bb = p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, nds);
+                    x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+                  }
+                }
+                if (j + 1 < c1) load_p_half(j + 1, h2);  // these registers are free again: next step's P
+              }
+              // 64 keys x 2 bytes = 4 chunks of 32 bytes per row; after the transpose every 256-bit store
+              // instruction of the warp writes whole 128-byte lines
+              transpose_chunks32_4x4(x, lane);
+              if (tile_valid) {
+                uint16_t* dst = ws_row + (mode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) st_global_v8(dst + r * p.ws_pitch, &x[8 * r]);
               }
             }
-          } else {
-            const uint32_t* pw = &pq[h2 * 32];
-            if (full) {
-#pragma unroll
-              for (int i = 0; i < 64; i += 2) {
-                const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
-                x[i >> 1] = pack2<false>(p0 * fmaf(__uint_as_float(s[i]), p.scale, stat),
-                                         p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, stat));
-              }
-            } else {
-              // P is already 0 where masked; the select only guards against non-finite dP of rows / keys
-              // outside the sequence
-#pragma unroll
-              for (int i = 0; i < 64; i += 2) {
-                const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
-                const float a = p0 * fmaf(__uint_as_float(s[i]), p.scale, stat);
-                const float bb = p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, stat);
-                x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
-              }
-            }
-            if (j + 1 < t.n_steps) load_p_half(j + 1, h2);  // these registers are free again: next step's P
-          }
-          // 64 keys x 2 bytes = 4 chunks of 32 bytes per row; after the transpose every 256-bit store
-          // instruction of the warp writes whole 128-byte lines
-          transpose_chunks32_4x4(x, lane);
-          if (tile_valid) {
-            uint16_t* dst = ws_row + (kMode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
-#pragma unroll
-            for (int r = 0; r < 4; ++r) st_global_v8(dst + r * p.ws_pitch, &x[8 * r]);
           }
         }
       }
@@ -418,42 +441,33 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
   }
 }
 
-template <int kMode>
-static int launch_pass(const splitd_params* p, const BwdParams& bp, cudaStream_t stream) {
-  const TileGeom& g = bp.g;
-  CUtensorMap tm_a, tm_b;
-  if (kMode == 0) {
-    if (int e = make_q_tmap(&tm_a, p->q, p, g, p->q_strides, 2 * g.pos_per_cta, "q")) return e;
-    if (int e = make_kv_tmap(&tm_b, p->k, p, p->k_strides, 128, "k")) return e;
-  } else {
-    if (int e = make_q_tmap(&tm_a, p->dout, p, g, p->do_strides, 2 * g.pos_per_cta, "dout")) return e;
-    if (int e = make_kv_tmap(&tm_b, p->v, p, p->v_strides, 128, "v")) return e;
-  }
-  const bool varlen = p->cu_seqlens_q != nullptr;
-  const int ppu = varlen ? (g.row_tiles + g.batch + 1) / 2 : (g.row_tiles + 1) / 2;
-  const long long pairs = static_cast<long long>(ppu) * g.head_units * (varlen ? 1 : g.batch);
-  if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "P/dS grid out of range");
-  auto kern = splitd_bwd_pds2_kernel<kMode>;
-  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pds2::kSmemBytes);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(pds2): %s", cudaGetErrorString(ce));
-  static int cache[64] = {};
-  const int resident = resident_cluster_pairs(kern, pds2::kThreads, pds2::kSmemBytes, cache);
-  const long long grid_pairs = pairs < resident ? pairs : resident;
-  ce = cudaMemsetAsync(bp.tile_counters + (kMode ? kCounterPds2 : kCounterPds), 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
-  kern<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(pds2::kThreads), pds2::kSmemBytes, stream>>>(
-      tm_a, tm_b, bp, static_cast<int>(pairs), ppu);
-  ce = cudaGetLastError();
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "P/dS launch failed: %s", cudaGetErrorString(ce));
-  return 0;
-}
-
 int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream) {
   BwdParams bp;
   if (int e = fill_bwd_params(p, bp)) return e;
   if (int e = check_workspace(p)) return e;
-  if (int e = launch_pass<0>(p, bp, stream)) return e;
-  return launch_pass<1>(p, bp, stream);
+  const TileGeom& g = bp.g;
+  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, 2 * g.pos_per_cta, "q")) return e;
+  if (int e = make_q_tmap(&tm_do, p->dout, p, g, p->do_strides, 2 * g.pos_per_cta, "dout")) return e;
+  if (int e = make_kv_tmap(&tm_k, p->k, p, p->k_strides, 128, "k")) return e;
+  if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 128, "v")) return e;
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  const int ppu = varlen ? (g.row_tiles + g.batch + 1) / 2 : (g.row_tiles + 1) / 2;
+  const long long pairs = static_cast<long long>(ppu) * g.head_units * (varlen ? 1 : g.batch);
+  if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "P/dS grid out of range");
+  cudaError_t ce =
+      cudaFuncSetAttribute(splitd_bwd_pds2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pds2::kSmemBytes);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(pds2): %s", cudaGetErrorString(ce));
+  static int cache[64] = {};
+  const int resident = resident_cluster_pairs(splitd_bwd_pds2_kernel, pds2::kThreads, pds2::kSmemBytes, cache);
+  const long long grid_pairs = pairs < resident ? pairs : resident;
+  ce = cudaMemsetAsync(bp.tile_counters + kCounterPds, 0, sizeof(int), stream);
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
+  splitd_bwd_pds2_kernel<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(pds2::kThreads), pds2::kSmemBytes,
+                           stream>>>(tm_q, tm_do, tm_k, tm_v, bp, static_cast<int>(pairs), ppu);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "P/dS launch failed: %s", cudaGetErrorString(ce));
+  return 0;
 }
 
 }  // namespace sd

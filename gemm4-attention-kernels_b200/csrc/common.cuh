@@ -74,7 +74,7 @@ struct BwdParams {
   int* tile_counters;     // kWsCounterBytes at the end of the workspace: work counters of the persistent kernels
 };
 constexpr int kWsCounterBytes = 256;
-constexpr int kCounterPds = 0, kCounterPds2 = 16, kCounterGrad = 32;  // int offsets, 64 bytes apart
+constexpr int kCounterPds = 0, kCounterGrad = 32;  // int offsets, 128 bytes apart
 
 // Which tile does this CTA pair work on. Returns false when the pair has nothing to do.
 struct TileCoord {
