@@ -130,9 +130,9 @@ int splitd_bwd_dkdv(const splitd_params* p, void* stream);
 /* The two steps splitd_bwd is made of after the preprocess step, for callers that want to time or schedule
  * them separately (no counterpart in the reference, whose kernels recompute instead):
  * splitd_bwd_tiles writes the bf16 P and dS tiles to `workspace` (S = QK^T and dP = dO V^T on the tensor
- * cores; two launches, P first; SPLITD_PDS_ONE_PASS=1 in the environment selects a single-launch form that
- * moves less through HBM and is a little slower); splitd_bwd_grads computes dq, dk and dv from them in one
- * launch. */
+ * cores, as two alternating GEMM passes; SPLITD_PDS_ONE_PASS=1 in the environment selects a kernel that does
+ * both GEMMs per key block instead and is a little slower); splitd_bwd_grads computes dq, dk and dv from them
+ * in one launch. */
 int splitd_bwd_tiles(const splitd_params* p, void* stream);
 int splitd_bwd_grads(const splitd_params* p, void* stream);
 
