@@ -8,7 +8,7 @@
 // MMA for 4 KB of streamed B operand per CTA instead of 64 cycles, i.e. half the K/V bytes per FLOP of the
 // one-pass kernel (bwd_pds_kernel.cu), whose speed is set by that stream.
 // Why they alternate: a pair runs pass 0 over a chunk of kChunkSteps key steps and then pass 1 over the same
-// chunk, so the P values pass 1 reads (<= 1 MB per pair) are still in L2 and HBM sees each tile element twice
+// chunk, so the P values pass 1 reads (<= 0.5 MB per pair) are still in L2 and HBM sees each tile element twice
 // (P out, dS out) like in the one-pass kernel. The resident operand is swapped at every pass switch, block by
 // block as the previous pass's last step releases it.
 //
@@ -29,7 +29,7 @@ namespace sd {
 
 namespace pds2 {
 constexpr int kStepKeys = 256;
-constexpr int kChunkSteps = 8;       // key steps per pass before the pair switches to the other pass
+constexpr int kChunkSteps = 4;       // key steps per pass before the pair switches to the other pass
 constexpr int kStages = 6;
 constexpr int kStageBytes = 16384;   // this CTA's 128 keys x 64 of the 512 D columns
 constexpr int kABlockBytes = 16384;  // the tile's 128 rows x the same 64 D columns
