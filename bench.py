@@ -322,6 +322,42 @@ def run_ours(args):
     e2e_ms = sharding.max_over_ranks(s0.elapsed_time(s1), dev)
     e2e_val = world * total_flops * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_steps else None
 
+    # ---- the two other GPU configurations of the reference's plan, timed once outside the step (N=1 only):
+    #      the packed causal training step (sequence lengths uniform in [128, 8192], 32768 tokens, seed 0) and
+    #      one (batch, kv-head group) shard of the B=2, S=32768, Hq=32, Hkv=4 causal layer (B=1, Hq=8, Hkv=1).
+    other = None
+    if rank == 0 and world == 1 and not args.skip_e2e:
+        del q, k, v, do
+        torch.cuda.empty_cache()
+        other = {}
+
+        def time_case(name, mk, hq, hkv, flops, **kw):
+            qq, kk, vv, dd = mk(hq), mk(hkv), mk(hkv), mk(hq)
+            res = []
+            for it in range(3):
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record()
+                out, lse = I._flash_attn_fwd(qq, kk, vv, causal=True, return_lse=True, **kw)
+                e1.record()
+                I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=True, **kw)
+                e2.record()
+                torch.cuda.synchronize(dev)
+                res.append((e0.elapsed_time(e1), e1.elapsed_time(e2)))
+            tf, tb = min(r[0] for r in res[1:]), min(r[1] for r in res[1:])
+            other[name] = {"fwd_ms": tf, "bwd_ms": tb, "fwd_tflops": flops / tf / 1e9, "bwd_tflops": 2.5 * flops / tb / 1e9}
+
+        gen, lens = torch.Generator().manual_seed(0), []
+        while sum(lens) < 32768:
+            lens.append(int(torch.randint(128, 8193, (1,), generator=gen)))
+        lens[-1] -= sum(lens) - 32768
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        time_case("packed_causal_32768_tokens", lambda h: torch.randn(32768, h, D, device=dev).to(torch.bfloat16),
+                  HQ, HKV, sum(4.0 * HQ * n * n * D for n in lens) * 0.5,
+                  cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+        other["packed_causal_32768_tokens"]["sequence_lengths"] = lens
+        time_case("shard_B1_S32768_Hq8_Hkv1_causal", lambda h: torch.randn(1, 32768, h, D, device=dev).to(torch.bfloat16),
+                  8, 1, 4.0 * 8 * 32768 * 32768 * D * 0.5)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.skip_e2e:
         fl, dt = cpu_sample()
@@ -341,7 +377,7 @@ def run_ours(args):
             "frac_of_sustained": {"fwd": fwd_tflops / peak_sus, "bwd": bwd_tflops / peak_sus},
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": launches, "clocks": clocks.summary(), "sweep": sweep,
+            "gpu_launches": launches, "clocks": clocks.summary(), "sweep": sweep, "other_configs": other,
             "context_sm90_readme": {"fwd_tflops": 270, "bwd_tflops": 100},
         }
         print(json.dumps(line))
