@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports ``attention_ref`` (fp32 attention with autograd) and ``attention_ref_pt`` (16-bit yardstick)
 from the reference's test module splitd-flash-attn/tests/test_flash_fwd_splitd_sdpa.py:132-185, runs
@@ -10,7 +10,7 @@ them on seeded inputs and stores inputs as seeds only + outputs as fp16-compress
 The fixtures are small (head_dim is fixed at 512 by the path, so sequence lengths are kept short).
 
 Cases
-  cfg1      : BASELINE config 1 -- B=1, S=256, Hq=8, Hkv=1, fp32 N(0,1) inputs, seed 0, non-causal
+  cfg1      : the CPU plumbing configuration -- B=1, S=256, Hq=8, Hkv=1, fp32 N(0,1) inputs, seed 0, non-causal
   gqa_causal: B=2, Sq=113, Sk=203, Hq=4, Hkv=2, causal (bottom-right aligned), seed 42
   mha_tail  : B=1, Sq=64,  Sk=128, Hq=2, Hkv=2, causal, seed 7
 Outputs: out, lse (logsumexp of masked scaled scores, test :562-571), dq, dk, dv from autograd.
@@ -77,4 +77,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

@@ -78,7 +78,7 @@ def test_bwd_deterministic():
 
 
 def test_config1_against_reference_golden():
-    """BASELINE config 1 (B=1,S=256,Hq=8,Hkv=1, seed 0): CUDA result on the bf16-rounded inputs vs the
+    """The CPU plumbing configuration of the reference plan (B=1,S=256,Hq=8,Hkv=1, seed 0): CUDA result on the bf16-rounded inputs vs the
     fp32 golden vectors of the reference's attention_ref + autograd (tests/golden/cfg1.npz)."""
     import os
 

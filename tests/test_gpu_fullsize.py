@@ -1,4 +1,4 @@
-"""GPU parity at the BASELINE configurations' full sizes.
+"""GPU parity at the full sizes of the reference plan's configurations.
 
 The fp32 oracle on a whole B*S = 16384 problem would need hours on a CPU, so these tests (a) run the oracle
 ON THE GPU (it is device agnostic) for one sampled (batch, KV-head group) shard -- shards are independent, so
@@ -26,7 +26,7 @@ def _inputs(B, S, seed):
 @pytest.mark.parametrize("B,S", [(16, 1024), (4, 4096), (1, 16384)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_sweep_shapes_forward_backward_shard_parity(B, S, causal):
-    """BASELINE configs 2 and 3 (forward / backward sweep shapes): one (batch, kv-group) shard vs the oracle."""
+    """The forward / backward sweep shapes: one (batch, kv-group) shard vs the oracle."""
     from splitd_flash_attn import split_flash_attn_func
 
     q, k, v, do = _inputs(B, S, seed=S + causal)
@@ -69,7 +69,7 @@ def test_softmax_rows_sum_to_one_and_linearity(B, S, causal):
 
 
 def test_config4_varlen_training_step_full_size():
-    """BASELINE config 4: packed causal fwd+bwd, lengths uniform-integer in [128, 8192] from a seed until the
+    """The packed training-step configuration: packed causal fwd+bwd, lengths uniform-integer in [128, 8192] from a seed until the
     total reaches 32768 tokens (last sequence truncated), Hq=32, Hkv=4. Two sampled sequences are checked
     against the oracle per (sequence, kv group); everything must be finite."""
     from splitd_flash_attn import split_flash_attn_varlen_func
@@ -107,7 +107,7 @@ def test_config4_varlen_training_step_full_size():
 
 
 def test_config5_layer_shards_equal_full_layer():
-    """BASELINE config 5 sharding rule at a reduced sequence length: the 8 (batch, kv-group) shards of a
+    """The 8-GPU layer configuration's sharding rule at a reduced sequence length: the 8 (batch, kv-group) shards of a
     B=2, Hq=32, Hkv=4 causal layer, run as independent calls on strided views, reproduce the unsharded
     result bit for bit (forward and backward)."""
     from splitd_flash_attn import sharding, split_flash_attn_func

@@ -1,6 +1,6 @@
 """GPU parity of the packed (varlen) layout, forward and backward, with ARBITRARY sequence lengths
 (the reference rounds lengths to multiples of 64 in its varlen backward test,
-tests/test_flash_fwd_splitd_sdpa.py:995-1002; BASELINE config 4 draws unrounded lengths)."""
+tests/test_flash_fwd_splitd_sdpa.py:995-1002; the packed training-step configuration draws unrounded lengths)."""
 import pytest
 import torch
 
@@ -86,7 +86,7 @@ def test_varlen_different_q_and_k_lengths():
 
 
 def test_varlen_config4_shape_reduced():
-    """BASELINE config 4 packing rule (uniform-integer lengths from a seed until the total is reached,
+    """The packed training-step configuration's packing rule (uniform-integer lengths from a seed until the total is reached,
     last sequence truncated) at a reduced total so the oracle finishes in seconds."""
     from splitd_flash_attn import split_flash_attn_varlen_func
 
