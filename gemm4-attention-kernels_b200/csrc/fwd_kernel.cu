@@ -98,6 +98,25 @@ __device__ __forceinline__ bool fwd_next_tile(const FwdParams& p, int r, int pai
   return true;
 }
 
+// A tile with at least one KV step, as the producer and the MMA issuer see it.
+struct FwdWork {
+  TileCoord tc;
+  int r, step0, n_steps, last_chunks;
+};
+
+// First round >= r_from in which this pair has a tile with work; false when the pair's list is exhausted.
+__device__ __forceinline__ bool fwd_find_work(const FwdParams& p, int r_from, int pair, int n_pairs, FwdWork& w) {
+  bool valid;
+  w.last_chunks = 4;
+  for (int r = r_from; fwd_next_tile(p, r, pair, n_pairs, w.tc, w.step0, w.n_steps, valid, &w.last_chunks); ++r) {
+    if (valid && w.n_steps > 0) {
+      w.r = r;
+      return true;
+    }
+  }
+  return false;
+}
+
 template <bool kFp16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
 splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -181,72 +200,85 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         stage = s;
         ++it;
       };
-      TileCoord tc;
-      int step0, n_steps, last_chunks = 4;
-      bool valid;
       const long long tp0 = prof ? clock64() : 0;
-      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid, &last_chunks); ++r) {
-        if (!valid || n_steps == 0) continue;
-        const int kb = g.cu_k ? 0 : tc.b;
-        // Q: two ring acquisitions (4 D blocks of 8 KB each) that stay resident for the whole tile
-        {
-          const int qpos = tc.q_off + tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
-          const int qb = g.cu_q ? 0 : tc.b;
-          uint32_t newq = 0;
-          for (int u = 0; u < 2 && ok; ++u) {
-            uint32_t st, bar, stage;
-            acquire(st, bar, stage);
-            if (!ok) break;
-            if (elect_one()) {
-              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+      // Q: two ring acquisitions (4 D blocks of 8 KB each) that stay resident for the whole tile
+      auto load_q = [&](const FwdWork& w) {
+        const int qpos = w.tc.q_off + w.tc.p0 + static_cast<int>(rank) * g.pos_per_cta;
+        const int qb = g.cu_q ? 0 : w.tc.b;
+        uint32_t newq = 0;
+        for (int u = 0; u < 2 && ok; ++u) {
+          uint32_t st, bar, stage;
+          acquire(st, bar, stage);
+          if (!ok) break;
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
 #pragma unroll
-              for (int d = 0; d < 4; ++d)
-                tma_load_5d_pair(st + d * 8192, &tm_q, bar, (u * 4 + d) * 64, 0, qpos, tc.hu, qb);
-            }
-            __syncwarp();
-            newq = slot_set(newq, u, slot_get(rs, stage));
-            rs = slot_set(rs, stage, slot_get(qs, u));  // the previous tile's Q slot joins the ring here
+            for (int d = 0; d < 4; ++d)
+              tma_load_5d_pair(st + d * 8192, &tm_q, bar, (u * 4 + d) * 64, 0, qpos, w.tc.hu, qb);
           }
-          qs = newq;
+          __syncwarp();
+          newq = slot_set(newq, u, slot_get(rs, stage));
+          rs = slot_set(rs, stage, slot_get(qs, u));  // the previous tile's Q slot joins the ring here
         }
-        auto load_k = [&](int j) {  // this CTA's 128 key rows of the step, 128 of the 512 D columns per stage
-          const int key0 = tc.k_off + (step0 + j) * kStepKeys + static_cast<int>(rank) * 128;
-          for (int c = 0; c < 4 && ok; ++c) {
-            uint32_t st, bar, stage;
-            acquire(st, bar, stage);
-            if (!ok) break;
-            if (elect_one()) {
-              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
-              tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, tc.hkv, kb);
-              tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, tc.hkv, kb);
-            }
-            __syncwarp();
+        qs = newq;
+      };
+      // this CTA's 128 key rows of a step (first key `key`), 128 of the 512 D columns per stage
+      auto load_k = [&](int b, int hkv, int key) {
+        const int kb = g.cu_k ? 0 : b;
+        const int key0 = key + static_cast<int>(rank) * 128;
+        for (int c = 0; c < 4 && ok; ++c) {
+          uint32_t st, bar, stage;
+          acquire(st, bar, stage);
+          if (!ok) break;
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+            tma_load_4d_pair(st, &tm_k, bar, (2 * c) * 64, key0, hkv, kb);
+            tma_load_4d_pair(st + 16384, &tm_k, bar, (2 * c + 1) * 64, key0, hkv, kb);
           }
-        };
-        auto load_v = [&](int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
-          const int n_kq = j == n_steps - 1 ? last_chunks : 4;
-          for (int kq = 0; kq < n_kq && ok; ++kq) {
-            uint32_t st, bar, stage;
-            acquire(st, bar, stage);
-            if (!ok) break;
-            const int key0 = tc.k_off + (step0 + j) * kStepKeys + kq * 64;
-            if (elect_one()) {
-              if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
+          __syncwarp();
+        }
+      };
+      auto load_v = [&](const FwdWork& w, int j) {  // 64 keys per stage, this CTA's 2 x 128 V columns (both accumulators)
+        const int kb = g.cu_k ? 0 : w.tc.b;
+        const int n_kq = j == w.n_steps - 1 ? w.last_chunks : 4;
+        for (int kq = 0; kq < n_kq && ok; ++kq) {
+          uint32_t st, bar, stage;
+          acquire(st, bar, stage);
+          if (!ok) break;
+          const int key0 = w.tc.k_off + (w.step0 + j) * kStepKeys + kq * 64;
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
 #pragma unroll
-              for (int m = 0; m < 2; ++m) {
-                const int dv0 = m * 256 + static_cast<int>(rank) * 128;
-                tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, tc.hkv, kb);
-                tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, tc.hkv, kb);
-              }
+            for (int m = 0; m < 2; ++m) {
+              const int dv0 = m * 256 + static_cast<int>(rank) * 128;
+              tma_load_4d_pair(st + m * 16384, &tm_v, bar, dv0, key0, w.tc.hkv, kb);
+              tma_load_4d_pair(st + m * 16384 + 8192, &tm_v, bar, dv0 + 64, key0, w.tc.hkv, kb);
             }
-            __syncwarp();
           }
-        };
-        load_k(0);
-        for (int j = 0; j < n_steps && ok; ++j) {
-          if (j + 1 < n_steps) load_k(j + 1);
-          load_v(j);
+          __syncwarp();
         }
+      };
+      // Ring order = the MMA issuer's order: the operands of the NEXT QK^T product (of this tile, or Q and the
+      // first K step of the next tile) go in front of the V rows of the current step.
+      FwdWork cur, nxt;
+      bool have = fwd_find_work(p, 0, pair_id, n_pairs, cur);
+      if (have) {
+        load_q(cur);
+        load_k(cur.tc.b, cur.tc.hkv, cur.tc.k_off + cur.step0 * kStepKeys);
+      }
+      while (have && ok) {
+        const bool has_next = fwd_find_work(p, cur.r + 1, pair_id, n_pairs, nxt);
+        for (int j = 0; j < cur.n_steps && ok; ++j) {
+          if (j + 1 < cur.n_steps) {
+            load_k(cur.tc.b, cur.tc.hkv, cur.tc.k_off + (cur.step0 + j + 1) * kStepKeys);
+          } else if (has_next) {
+            load_q(nxt);
+            load_k(nxt.tc.b, nxt.tc.hkv, nxt.tc.k_off + nxt.step0 * kStepKeys);
+          }
+          load_v(cur, j);
+        }
+        cur = nxt;
+        have = has_next;
       }
       if (prof && lane == 0) {
         p.debug[32] = static_cast<float>(t_a);
@@ -270,92 +302,100 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t rs = 0x3210u, qs = 0x54u;  // same slot tables as the producer's
       bool ok = true;
       t_all = prof ? clock64() : 0;
-      TileCoord tc;
-      int step0, n_steps, last_chunks = 4;
-      bool valid;
       // wait on a barrier with all lanes, keep the outcome warp-uniform
       auto wait_all = [&](uint32_t bar, uint32_t parity, bool cluster_scope) {
         bool w = cluster_scope ? mbar_wait<true>(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA)
                                : mbar_wait(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA);
         return __all_sync(0xffffffffu, w);
       };
-      for (int r = 0; ok && fwd_next_tile(p, r, pair_id, n_pairs, tc, step0, n_steps, valid, &last_chunks); ++r) {
-        if (!valid || n_steps == 0) continue;
-        // Q of this tile: wait for its two ring entries, hand the previous tile's Q slots to the ring
-        uint32_t q_lo[2];
-        {
-          uint32_t newq = 0;
-          for (int u = 0; u < 2 && ok; ++u) {
-            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
-            if (!ok) break;
-            newq = slot_set(newq, u, slot_get(rs, s));
-            rs = slot_set(rs, s, slot_get(qs, u));
-            if (elect_one()) umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);  // old Q slot is free once all earlier MMAs are done
-            __syncwarp();
-            ++it;
-          }
-          if (!ok) break;
-          qs = newq;
-          q_lo[0] = desc_lo(sSlots + slot_get(qs, 0) * kStageBytes, 16);
-          q_lo[1] = desc_lo(sSlots + slot_get(qs, 1) * kStageBytes, 16);
+      uint32_t q_lo[2] = {0, 0};
+      // Q of a tile: wait for its two ring entries, hand the previous tile's Q slots to the ring
+      auto take_q = [&]() {
+        uint32_t newq = 0;
+        for (int u = 0; u < 2 && ok; ++u) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
+          if (!ok) return;
+          newq = slot_set(newq, u, slot_get(rs, s));
+          rs = slot_set(rs, s, slot_get(qs, u));
+          if (elect_one()) umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);  // old Q slot is free once all earlier MMAs are done
+          __syncwarp();
+          ++it;
         }
-        auto issue_s = [&](uint32_t step) {
-          const uint32_t d_tmem = tmem_base + kTmemColsS + (step & 1) * 128;
+        qs = newq;
+        q_lo[0] = desc_lo(sSlots + slot_get(qs, 0) * kStageBytes, 16);
+        q_lo[1] = desc_lo(sSlots + slot_get(qs, 1) * kStageBytes, 16);
+      };
+      auto issue_s = [&](uint32_t step) {
+        const uint32_t d_tmem = tmem_base + kTmemColsS + (step & 1) * 128;
 #pragma unroll 1
-          for (int c = 0; c < 4 && ok; ++c) {
-            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-            const long long t0 = prof ? clock64() : 0;
-            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
-            if (prof) t_a += clock64() - t0;
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t a0 = (c < 2 ? q_lo[0] : q_lo[1]) + (((c & 1) * 16384) >> 4);
-            const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 16);
-            if (elect_one()) {
+        for (int c = 0; c < 4 && ok; ++c) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
+          ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
+          if (prof) t_a += clock64() - t0;
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a0 = (c < 2 ? q_lo[0] : q_lo[1]) + (((c & 1) * 16384) >> 4);
+          const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 16);
+          if (elect_one()) {
 #pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;   // A: 8 KB per 64-wide D block
-                const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;  // B: 16 KB per 64-wide D block
-                umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc_s, (c | k) != 0);
-              }
-              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-              if (c == 3) umma_commit_pair(ctrl + kBarSFull + 8 * (step & 1), 3);
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t offa = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;   // A: 8 KB per 64-wide D block
+              const uint32_t offb = ((k >> 2) * 16384 + (k & 3) * 32) >> 4;  // B: 16 KB per 64-wide D block
+              umma_ss<2>(d_tmem, desc_join(a0 + offa), desc_join(b0 + offb), idesc_s, (c | k) != 0);
             }
-            __syncwarp();
-            ++it;
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            if (c == 3) umma_commit_pair(ctrl + kBarSFull + 8 * (step & 1), 3);
           }
-        };
-        auto issue_pv = [&](int j) {
-          const int n_kq = j == n_steps - 1 ? last_chunks : 4;
+          __syncwarp();
+          ++it;
+        }
+      };
+      auto issue_pv = [&](int j, int n_kq) {
 #pragma unroll 1
-          for (int kq = 0; kq < n_kq && ok; ++kq) {
-            const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-            const long long t0 = prof ? clock64() : 0;
-            ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
-            if (prof) t_b += clock64() - t0;
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t a0 = p_lo + kq * (8192 >> 4);
-            const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 8192);
-            if (elect_one()) {
+        for (int kq = 0; kq < n_kq && ok; ++kq) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          const long long t0 = prof ? clock64() : 0;
+          ok = wait_all(ctrl + kBarFull + 8 * s, ph, false);
+          if (prof) t_b += clock64() - t0;
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a0 = p_lo + kq * (8192 >> 4);
+          const uint32_t b0 = desc_lo(sSlots + slot_get(rs, s) * kStageBytes, 8192);
+          if (elect_one()) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < 4; ++k) {
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
-                  umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
-                             desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
-              }
-              umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
-              if (kq == n_kq - 1) umma_commit_pair(ctrl + kBarPvDone, 3);
+              for (int m = 0; m < 2; ++m)
+                umma_ss<2>(tmem_base + kTmemColsO + m * 128, desc_join(a0 + ((k * 32) >> 4)),
+                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc_pv, (j | kq | k) != 0);
             }
-            __syncwarp();
-            ++it;
+            umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
+            if (kq == n_kq - 1) umma_commit_pair(ctrl + kBarPvDone, 3);
           }
-        };
-        issue_s(gs);
-        for (int j = 0; j < n_steps && ok; ++j) {
-          if (j + 1 < n_steps) issue_s(gs + 1);
+          __syncwarp();
+          ++it;
+        }
+      };
+      // Every iteration issues the NEXT QK^T product first (the next step of this tile, or the first step of
+      // the pair's next tile) and then the PV product of the current step, so the softmax warps always find
+      // the next scores ready and the tensor pipe has work while they are busy, across tile switches too.
+      FwdWork cur, nxt;
+      bool have = fwd_find_work(p, 0, pair_id, n_pairs, cur);
+      if (have) {
+        take_q();
+        if (ok) issue_s(gs);
+      }
+      while (have && ok) {
+        const bool has_next = fwd_find_work(p, cur.r + 1, pair_id, n_pairs, nxt);
+        for (int j = 0; j < cur.n_steps && ok; ++j) {
+          if (j + 1 < cur.n_steps) {
+            issue_s(gs + 1);
+          } else if (has_next) {
+            take_q();
+            if (ok) issue_s(gs + 1);
+          }
           if (!ok) break;
           const long long t0 = prof ? clock64() : 0;
           ok = wait_all(ctrl + kBarPFull, gs & 1, true);
@@ -364,10 +404,12 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (prof) t_c += clock64() - t0;
           if (!ok) break;
           tc_fence_after_sync();
-          issue_pv(j);
+          issue_pv(j, j == cur.n_steps - 1 ? cur.last_chunks : 4);
           ++gs;
         }
         ++tiles;
+        cur = nxt;
+        have = has_next;
       }
       if (prof && lane == 0) {
         p.debug[34] = static_cast<float>(gs);
@@ -385,7 +427,8 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int xi = wg * 128 + L;            // slot in the exchange arrays
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t xbar = ctrl + kBarXchg + 8 * (q & 1);
-    const int grp_row0 = row & ~7;          // first row of this lane's group of 8 (epilogue stores)
+    const int grp_row0 = row & ~3;          // first row of this lane's group of 4 (epilogue stores)
+    const int pack_shift = 31 - __clz(g.pack_g);  // heads fold into rows only when the group is a power of two
     uint32_t xphase = 0;
     uint32_t gs = 0;                        // KV steps seen so far (same counter as the MMA issuer's)
     bool ok = true;
@@ -396,10 +439,100 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     t_all = prof ? clock64() : 0;
     long long tph0 = 0, tph1 = 0, tph2 = 0, tph3 = 0, tph4 = 0, tph5 = 0, tph6 = 0;
 
-    for (int rr = 0; ok && fwd_next_tile(p, rr, pair_id, n_pairs, tc, step0, n_steps, valid); ++rr) {
-      if (!valid) continue;
-      const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + row / g.pack_g;
-      const int head = (g.pack_g > 1) ? tc.hu * g.pack_g + row % g.pack_g : tc.hu;
+    // Epilogue of a tile: O / rowsum -> global memory, LSE. `has_acc` is false for a tile without visible keys
+    // (zeros, LSE = -inf, no TMEM access). The caller has waited for the tile's last PV.
+    auto epilogue = [&](int e_b, int e_hu, int e_p0, int e_sq, int e_qoff, float m_ref, float l_sum, bool has_acc) {
+      const int pos = e_p0 + static_cast<int>(rank) * g.pos_per_cta + (row >> pack_shift);
+      const int head = e_hu * g.pack_g + (row & (g.pack_g - 1));
+      float l_tot = 0.f;
+      if (has_acc) {
+        // row sums of the four threads of a row
+        float* xs = xchg + xphase * 256;
+        xs[xi] = l_sum;
+        mbar_arrive(xbar);
+        ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
+        ok = __all_sync(0xffffffffu, ok);
+        xphase ^= 1u;
+        if (!ok) return;
+        l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
+      }
+      const bool any = l_tot > 0.f;
+      const float inv = any ? 1.f / l_tot : 0.f;
+      if (pos < e_sq && half == 0 && wg == 0 && p.lse != nullptr) {
+        const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+        const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
+        const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + e_qoff + pos
+                                   : (static_cast<int64_t>(e_b) * g.heads_q + head) * e_sq + pos;
+        p.lse[idx] = lse;
+      }
+      // Stores: each thread owns one row, so a plain store per thread would touch 32 different lines per warp
+      // instruction. 4 x 4 transposes of 32-byte chunks inside groups of 4 lanes make every store instruction
+      // write 8 full 128-byte lines instead. The four row addresses are computed once per tile.
+      uint16_t* obase = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : e_b * p.o_stride_b) + wg * 256 + half * 128 +
+                        (lane & 3) * 16;
+      uint16_t* rowp[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int re = grp_row0 + e;
+        const int pos_e = e_p0 + static_cast<int>(rank) * g.pos_per_cta + (re >> pack_shift);
+        const int head_e = e_hu * g.pack_g + (re & (g.pack_g - 1));
+        rowp[e] = pos_e < e_sq ? obase + static_cast<int64_t>(e_qoff + pos_e) * p.o_stride_s +
+                                     static_cast<int64_t>(head_e) * p.o_stride_h
+                               : nullptr;
+      }
+#pragma unroll 1
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t t[64];
+        if (has_acc) {
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
+          tmem_ld_wait();
+          if (c2 == 1) {  // O has been read: the next tile's first PV may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_o_free);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) t[i] = 0u;
+        }
+        // a row without a visible key has P = 0 throughout, so its accumulator is 0 and inv = 0 keeps it so
+        uint32_t x[32];
+#pragma unroll
+        for (int i = 0; i < 64; i += 2)
+          x[i >> 1] = pack2<kFp16>(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+        transpose_chunks32_4x4(x, lane);
+        // now x[8e..8e+7] = 32-byte chunk (lane & 3) of row grp_row0 + e
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (rowp[e] != nullptr) st_global_32b(rowp[e] + c2 * 64, &x[8 * e]);
+      }
+    };
+
+    int prev_b = 0, prev_hu = 0, prev_p0 = 0, prev_sq = 0, prev_qoff = 0;  // what the owed epilogue needs of its tile
+    float prev_m = 0.f, prev_l = 0.f;
+    bool have_prev = false;  // a tile whose steps are done but whose epilogue has not run yet
+    long long t_epi = 0;
+
+    for (int rr = 0; ok; ++rr) {
+      const bool more = fwd_next_tile(p, rr, pair_id, n_pairs, tc, step0, n_steps, valid);
+      if (more && !valid) continue;
+      if (!more || n_steps == 0) {
+        // End of the list, or a tile without a visible key: first the epilogue that is still owed, then
+        // (for such a tile) zeros and LSE = -inf.
+        if (have_prev) {
+          ok = mbar_wait(ctrl + kBarPvDone, (gs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          have_prev = false;
+          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_l, true);
+        }
+        if (more && ok) epilogue(tc.b, tc.hu, tc.p0, tc.sq, tc.q_off, -INFINITY, 0.f, false);
+        if (!more) break;
+        continue;
+      }
+      const int pos = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + (row >> pack_shift);
       int limit = tc.sk - 1;  // last visible key of this row
       if (p.win_right >= 0) limit = min(limit, pos + tc.sk - tc.sq + p.win_right);
       const int lo_limit = p.win_left >= 0 ? pos + tc.sk - tc.sq - p.win_left : 0;  // first visible key
@@ -443,7 +576,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
         if (prof) { const long long q1 = clock64(); tph1 += q1 - q0; q0 = q1; }
         // combine with the three other threads that hold parts of this row
-        float* xs = xchg + (gs & 1) * 256;
+        float* xs = xchg + xphase * 256;  // exchanges alternate between the two arrays
         xs[xi] = mx;
         t0 = prof ? clock64() : 0;
         mbar_arrive(xbar);
@@ -477,9 +610,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
 
         if (prof) { const long long q1 = clock64(); tph3 += q1 - q0; q0 = q1; }
-        // the P buffer and the O accumulators are free once PV of the previous step has completed
-        // (for the first step of a tile the epilogue of the previous tile already waited for it)
-        if (j > 0) {
+        // the P buffer and the O accumulators are free once PV of the previous step has completed (at the
+        // first step of a tile that is the last PV of the previous tile, whose epilogue is still to come)
+        if (j > 0 || have_prev) {
           t0 = prof ? clock64() : 0;
           ok = mbar_wait(ctrl + kBarPvDone, (gs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
           if (prof) t_c += clock64() - t0;
@@ -516,79 +649,33 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(leader_p_full);
         if (prof) { const long long q4 = clock64(); tph4 += q4 - q0; tph5 += q2 - q0; tph6 += q3 - q2; }
+        if (j == 0 && have_prev) {
+          // The previous tile's epilogue runs HERE, after this tile's first P block has been handed over:
+          // the tensor pipe works on the previous tile's last PV while the first softmax step runs, and on
+          // this tile's first PV (as soon as O has been read) while the stores of the epilogue drain.
+          const long long te = prof ? clock64() : 0;
+          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_l, true);
+          if (prof) t_epi += clock64() - te;
+          have_prev = false;
+          if (!ok) break;
+        }
       }
       if (!ok) break;
-
-      // ---- epilogue of this tile
-      float l_tot = 0.f;
-      if (n_steps > 0) {
-        ok = mbar_wait(ctrl + kBarPvDone, (gs - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        // row sums of the four threads of a row; the slot of the tile's last step is safe to reuse here
-        float* xs = xchg + ((gs - 1) & 1) * 256;
-        xs[xi] = l_sum;
-        mbar_arrive(xbar);
-        ok = mbar_wait(xbar, xphase, abort_flag, p.status, ST_TIMEOUT_PEER);
-        ok = __all_sync(0xffffffffu, ok);
-        xphase ^= 1u;
-        if (!ok) break;
-        l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
-      }
-      const bool any = l_tot > 0.f;
-      const float inv = any ? 1.f / l_tot : 0.f;
-      if (pos < tc.sq && half == 0 && wg == 0 && p.lse != nullptr) {
-        const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
-        const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
-        const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + tc.q_off + pos
-                                   : (static_cast<int64_t>(tc.b) * g.heads_q + head) * tc.sq + pos;
-        p.lse[idx] = lse;
-      }
-      // Stores: each thread owns one row, so a plain 16-byte store per thread would touch 32 different
-      // lines per warp instruction. 8 x 8 chunk transposes inside groups of 8 lanes make every store
-      // instruction write 4 full 128-byte lines instead.
-      uint16_t* obase = reinterpret_cast<uint16_t*>(p.o) + (g.cu_q ? 0 : tc.b * p.o_stride_b);
-#pragma unroll 1
-      for (int c2 = 0; c2 < 2; ++c2) {
-        uint32_t t[64];
-        if (n_steps > 0) {
-          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
-          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + c2 * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
-          tmem_ld_wait();
-          if (c2 == 1) {  // O has been read: the next tile's first PV may overwrite it
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(leader_o_free);
-          }
-        }
-        uint32_t x[32];
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float a = any ? __uint_as_float(t[i]) * inv : 0.f;
-          const float b = any ? __uint_as_float(t[i + 1]) * inv : 0.f;
-          x[i >> 1] = pack2<kFp16>(a, b);
-        }
-        transpose_chunks_8x8(x, lane);
-        // now x[4e..4e+3] = 16-byte chunk (lane & 7) of row grp_row0 + e
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int re = grp_row0 + e;
-          const int pos_e = tc.p0 + static_cast<int>(rank) * g.pos_per_cta + re / g.pack_g;
-          const int head_e = (g.pack_g > 1) ? tc.hu * g.pack_g + re % g.pack_g : tc.hu;
-          if (pos_e < tc.sq) {
-            uint16_t* dst = obase + static_cast<int64_t>(tc.q_off + pos_e) * p.o_stride_s +
-                            static_cast<int64_t>(head_e) * p.o_stride_h + wg * 256 + half * 128 + c2 * 64 + (lane & 7) * 8;
-            st_global_v4(dst, x[4 * e], x[4 * e + 1], x[4 * e + 2], x[4 * e + 3]);
-          }
-        }
-      }
+      prev_b = tc.b;
+      prev_hu = tc.hu;
+      prev_p0 = tc.p0;
+      prev_sq = tc.sq;
+      prev_qoff = tc.q_off;
+      prev_m = m_ref;
+      prev_l = l_sum;
+      have_prev = true;
     }
     if (prof && warp == 4 && lane == 0) {
       p.debug[40] = static_cast<float>(t_a);
       p.debug[41] = static_cast<float>(t_b);
       p.debug[42] = static_cast<float>(t_c);
       p.debug[43] = static_cast<float>(clock64() - t_all);
+      p.debug[44] = static_cast<float>(t_epi);
       p.debug[45] = static_cast<float>(tph0);
       p.debug[46] = static_cast<float>(tph1);
       p.debug[47] = static_cast<float>(tph2);
