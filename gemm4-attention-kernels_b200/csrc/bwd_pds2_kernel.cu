@@ -137,7 +137,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // optional cycle counters of one pair (debug[0..5]), summed over its tiles
   const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
   float* dbg = p.debug;
-  long long t_a = 0, t_b = 0, t_c = 0;
+  long long t_a = 0, t_b = 0, t_c = 0, t_m0 = 0, t_m1 = 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -324,17 +324,19 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // after the 4 x 4 chunk transposes a thread handles chunk (lane & 3) of rows (lane & ~3) + r, r = 0..3
       const int64_t row_delta0 = static_cast<int64_t>((lane & ~3) - lane) * p.ws_pitch;
 
-      // pass 1: the P values of this thread's 128 keys of a step, two per word: plain 32-byte loads of the
-      // thread's own row (whole sectors; only the stores need the chunk transposes). The values were stored by
-      // lanes of this same warp a chunk of steps ago (__syncwarp orders the two) and normally still sit in L2.
-      // Each 64-key half is re-loaded for the NEXT step as soon as this step is done with it, so the latency
-      // of the loads hides behind the rest of the step.
+      // pass 1: the P values of a step come back with the access pattern of the stores (lane l reads 32-byte
+      // chunk l & 3 of rows (l & ~3) + r: whole 128-byte lines per instruction, a quarter of the L1 wavefronts
+      // of own-row loads) and the same 4 x 4 transposes, which are their own inverse, put every thread's own row
+      // back together right before use. The values were stored by lanes of this same warp a chunk of steps ago
+      // (__syncwarp orders the two) and normally still sit in L2. Each 64-key half is re-loaded for the NEXT
+      // step as soon as this step is done with it, so the latency of the loads hides behind the rest of the step.
       uint32_t pq[64];
       auto load_p_half = [&](int step, int h2) {
+        const uint16_t* src = ws_row + row_delta0 + step * kStepKeys + ch * 128 + h2 * 64 + (lane & 3) * 16;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           if (tile_valid)
-            ld_global_v8(ws_row + step * kStepKeys + ch * 128 + h2 * 64 + r * 16, &pq[h2 * 32 + 8 * r]);
+            ld_global_v8(src + r * p.ws_pitch, &pq[h2 * 32 + 8 * r]);
           else
 #pragma unroll
             for (int i = 0; i < 8; ++i) pq[h2 * 32 + 8 * r + i] = 0u;
@@ -353,7 +355,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const int key_base = j * kStepKeys + ch * 128;
             const long long t0 = prof ? clock64() : 0;
             ok = mbar_wait(ctrl + kBarOutFull + 8 * b, (gs >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
-            if (prof) t_c += clock64() - t0;
+            const long long t1 = prof ? clock64() : 0;
+            if (prof) t_c += t1 - t0;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
@@ -388,7 +391,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                   }
                 }
               } else {
-                const uint32_t* pw = &pq[h2 * 32];
+                uint32_t(&pw)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pq[h2 * 32]);
+                transpose_chunks32_4x4(pw, lane);  // back to this thread's own row
                 if (full) {
 #pragma unroll
                   for (int i = 0; i < 64; i += 2) {
@@ -418,6 +422,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int r = 0; r < 4; ++r) st_global_v8(dst + r * p.ws_pitch, &x[8 * r]);
               }
             }
+            if (prof) (mode ? t_m1 : t_m0) += clock64() - t1;
           }
         }
       }
@@ -425,6 +430,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (prof && warp == 4 && lane == 0) {
       dbg[4] = static_cast<float>(t_c);
       dbg[5] = static_cast<float>(clock64() - t_begin);
+      dbg[6] = static_cast<float>(t_m0);  // busy cycles of the P steps / of the dS steps
+      dbg[7] = static_cast<float>(t_m1);
     }
   }
 
