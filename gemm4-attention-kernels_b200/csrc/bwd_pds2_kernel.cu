@@ -105,10 +105,10 @@ __device__ __forceinline__ bool pds2_decode(const BwdParams& p, int ppu, int idx
   return true;
 }
 
-__device__ __forceinline__ void ld_global_v8(const void* p, uint32_t* w) {
-  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+__device__ __forceinline__ void ld_global_v8_hint(const void* p, uint32_t* w, uint64_t policy) {
+  asm volatile("ld.global.L2::cache_hint.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8], %9;"
                : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
-               : "l"(p)
+               : "l"(p), "l"(policy)
                : "memory");
 }
 
@@ -296,6 +296,9 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const int64_t plane = p.ws_rows * p.ws_pitch;
     const uint32_t leader_free0 = mapa_u32(ctrl + kBarOutFree, 0);
+    // P is read back by this kernel a few microseconds after it is written, dS not before the next kernel:
+    // tell L2 which of the two to keep when it has to choose
+    const uint64_t pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
     bool ok = true;
     uint32_t gs = 0;
     const long long t_begin = prof ? clock64() : 0;
@@ -336,7 +339,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           if (tile_valid)
-            ld_global_v8(src + r * p.ws_pitch, &pq[h2 * 32 + 8 * r]);
+            ld_global_v8_hint(src + r * p.ws_pitch, &pq[h2 * 32 + 8 * r], pol_stream);  // read once: may go now
           else
 #pragma unroll
             for (int i = 0; i < 8; ++i) pq[h2 * 32 + 8 * r + i] = 0u;
@@ -419,7 +422,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               if (tile_valid) {
                 uint16_t* dst = ws_row + (mode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
 #pragma unroll
-                for (int r = 0; r < 4; ++r) st_global_v8(dst + r * p.ws_pitch, &x[8 * r]);
+                for (int r = 0; r < 4; ++r) st_global_v8_hint(dst + r * p.ws_pitch, &x[8 * r], mode ? pol_stream : pol_keep);
               }
             }
             if (prof) (mode ? t_m1 : t_m0) += clock64() - t1;

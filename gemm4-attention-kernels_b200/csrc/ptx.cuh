@@ -428,6 +428,23 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
                "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
                : "memory");
 }
+// L2 eviction priorities for data with a known lifetime: `keep` for lines that are read again soon, `stream`
+// for lines nobody reads again before they would be evicted anyway.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void st_global_v8_hint(void* p, const uint32_t* w, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(p), "r"(w[0]),
+               "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "l"(policy)
+               : "memory");
+}
 // 32 bytes to an address that is only known to be 16-byte aligned: one 256-bit store when it can be.
 __device__ __forceinline__ void st_global_32b(void* p, const uint32_t* w) {
   if ((reinterpret_cast<uintptr_t>(p) & 31u) == 0) {
