@@ -249,8 +249,8 @@ def run_ours(args):
     algo = {"fwd": total_fwd, "bwd_tiles": total_fwd, "bwd_grads": 1.5 * total_fwd}
     #      The forward's traffic is its operands and output once (0.274 GB at B*S = 4096), so it scales with
     #      B*S (x4 for every shape of the sweep), not with the FLOPs.
-    dram_bytes_per_flop = {"fwd": None, "bwd_tiles": 3.23e9 / 1.0995e12, "bwd_grads": 3.83e9 / (1.5 * 1.0995e12)}
-    fwd_dram_bytes_per_launch = 0.274e9 * (16384 / 4096)
+    dram_bytes_per_flop = {"fwd": None, "bwd_tiles": 3.126e9 / 1.0995e12, "bwd_grads": 3.83e9 / (1.5 * 1.0995e12)}
+    fwd_dram_bytes_per_launch = 0.266e9 * (16384 / 4096)
     dom = max(algo, key=lambda n: kt[n])
     achieved = algo[dom] * n_steps / kt[dom] / 1e9
     n_launch = len(cases)
