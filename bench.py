@@ -168,7 +168,10 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("SPLITD_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
+        # stdout carries the one JSON line only: NCCL's own output (its version banner is printed from level
+        # WARN up) goes to stderr
+        os.environ["NCCL_DEBUG"] = os.environ.get("SPLITD_NCCL_DEBUG", "WARN")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
