@@ -18,8 +18,8 @@
 // than 2^8 (the exact value is restored by the final 1/rowsum scaling).
 //
 // PERSISTENT pairs: the grid is one pair per SM pair; each pair walks over tiles (snake order over the
-// tile list, which keeps pairs balanced under causal masking and keeps concurrently running pairs on the
-// same K/V). Shared memory is six 32 KB slots + a 32 KB P buffer: a tile's Q occupies two slots, the K/V
+// tile list, whose blocks alternate between heaviest-first and lightest-first under a causal mask: that keeps
+// pairs balanced and keeps concurrently running pairs on the same K/V). Shared memory is six 32 KB slots + a 32 KB P buffer: a tile's Q occupies two slots, the K/V
 // ring four. Q is loaded like any other ring entry, so the NEXT tile's Q arrives in the first two ring
 // slots that the current tile's last PV frees, and at the tile switch the old Q slots join the ring: no
 // idle time for launch, TMEM allocation, barrier set-up or the Q load between tiles, and the epilogue of
@@ -80,6 +80,22 @@ __device__ __forceinline__ bool fwd_next_tile(const FwdParams& p, int r, int pai
   valid = idx < p.total_pairs && decode_tile(p.g, idx, tc);
   step0 = 0;
   n_steps = 0;
+  if (valid && p.g.causal) {
+    // decode_tile lists the row tiles of every (batch, head unit) block heaviest first. Walk every other block
+    // lightest first instead (the last block of the list always heaviest first): the weights along the list
+    // then have no jumps at the block borders, which is what the static round-robin assignment of the list to
+    // the pairs needs to come out balanced. With a jump, the pairs that draw the light end of one block in
+    // the round that crosses the border stay a heavy tile behind the others for good: 3-5 % at S >= 4096.
+    const int blk = p.g.cu_q ? tc.hu * p.g.batch + tc.b : tc.b * p.g.head_units + tc.hu;
+    if ((p.g.batch * p.g.head_units - 1 - blk) & 1) {
+      const int pos_per_pair = 2 * p.g.pos_per_cta;
+      const int nt = (tc.sq + pos_per_pair - 1) / pos_per_pair;
+      const int rt = nt - 1 - tc.rt;
+      tc.tile_global += rt - tc.rt;
+      tc.rt = rt;
+      tc.p0 = rt * pos_per_pair;
+    }
+  }
   if (valid) {
     // keys visible to row i: [i + sk - sq - win_left, i + sk - sq + win_right] (each side optional)
     int kv_hi = tc.sk, kv_lo = 0;
@@ -301,7 +317,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t tiles = 0;  // tiles with work done so far
       uint32_t rs = 0x3210u, qs = 0x54u;  // same slot tables as the producer's
       bool ok = true;
-      t_all = prof ? clock64() : 0;
+      t_all = p.debug != nullptr ? clock64() : 0;
       // wait on a barrier with all lanes, keep the outcome warp-uniform
       auto wait_all = [&](uint32_t bar, uint32_t parity, bool cluster_scope) {
         bool w = cluster_scope ? mbar_wait<true>(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA)
@@ -411,6 +427,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         cur = nxt;
         have = has_next;
       }
+      // longest-running pair of the launch in units of 1024 cycles, as an integer in debug[35]
+      if (p.debug != nullptr && lane == 0)
+        atomicMax(reinterpret_cast<int*>(p.debug + 35), static_cast<int>((clock64() - t_all) >> 10));
       if (prof && lane == 0) {
         p.debug[34] = static_cast<float>(gs);
         p.debug[36] = static_cast<float>(t_a);

@@ -83,7 +83,8 @@ typedef struct {
   int32_t* status_flag; /* may be NULL */
 
   /* optional fp32 device buffer of at least 64 elements receiving per-role cycle counters of one CTA pair
-     (tests / tuning only): [0,8) P/dS kernel, [8,16) gradient kernel, [32,52) forward kernel */
+     (tests / tuning only): [0,8) P/dS kernel, [8,16) gradient kernel, [32,52) forward kernel; element 35
+     holds, as an int32, the cycle count / 1024 of the forward's longest-running CTA pair (zero it first) */
   float* debug;
 
   /* ---- forward-only score modifiers (the backward rejects them, like src/interface.py:676-683) ---- */
