@@ -1,6 +1,8 @@
 """Build libsplitd_attn.so in-tree with nvcc for sm_100a.
 
-    python gemm4-attention-kernels_b200/build.py [--verbose]
+    python gemm4-attention-kernels_b200/build.py [--verbose] [--profile]
+
+--profile compiles the in-kernel cycle counters in (-DSPLITD_PROFILE; they are written to splitd_params::debug).
 
 nvcc cross-compiles without a GPU. The shared object lands next to the sources
 (csrc/libsplitd_attn.so) and is what splitd_flash_attn/_capi.py loads.
@@ -16,8 +18,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "libsplitd_attn.so")
-SOURCES = ["capi.cu", "fwd_kernel.cu", "bwd_preprocess.cu", "bwd_pds_kernel.cu",
-    "bwd_pds2_kernel.cu", "bwd_grad_kernel.cu", "no_alloc.cu"]
+SOURCES = ["capi.cu", "fwd_kernel.cu", "bwd_preprocess.cu", "bwd_pds2_kernel.cu", "bwd_grad_kernel.cu",
+           "no_alloc.cu", "wait_probe.cu"]
 
 
 def _nvcc() -> str:
@@ -36,7 +38,7 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, profile: bool = False) -> str:
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     if not force and not _stale():
         return OUT
@@ -55,6 +57,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     ]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    if profile:
+        cmd += ["-DSPLITD_PROFILE=1"]
     cmd += srcs
     res = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
     if verbose or res.returncode != 0:
@@ -65,4 +69,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force=True, verbose="--verbose" in sys.argv))
+    print(build(force=True, verbose="--verbose" in sys.argv, profile="--profile" in sys.argv))

@@ -1,5 +1,5 @@
-// Backward step 2b / 3: dQ, dK and dV as GEMMs over the bf16 P / dS tiles in the workspace
-// (bwd_pds_kernel.cu), for head_dim 512 on sm_100a.
+// Backward step 2b / 3: dQ, dK and dV as GEMMs over the fp16 P / dS tiles in the workspace
+// (bwd_pds2_kernel.cu), for head_dim 512 on sm_100a.
 //
 //   dV[keys, 512] = sum over packed rows  P^T  [keys, rows] * dO[rows, 512]
 //   dK[keys, 512] = sum over packed rows  dS^T [keys, rows] * Q [rows, 512]
@@ -17,13 +17,24 @@
 // per 64-deep contraction chunk, A = 16 KB (this CTA's 128 output rows) and B = 32 KB (this CTA's half
 // of the 512 output columns; the pair shares B through the 2-SM MMA).
 // Operand forms: P^T / dS^T are read straight from the [rows][keys] workspace as MN-major A; dS for dQ
-// is the same memory read as K-major A; dO, Q and K rows are MN-major B.
+// is the same memory read as K-major A; dO, Q and K rows are MN-major B. P and dS are fp16 (bwd_common.cuh) and
+// the two operands of one MMA must share a format, so B comes from the fp16 copies of dO, Q and K that the
+// preprocess step leaves in the workspace. The power-of-two scales of P, dS and dO are taken out of the fp32
+// accumulators before the final rounding to bf16.
 //
 // Persistent pairs: the grid is one pair per SM pair, each drawing output tiles (dV/dK tiles first, then
-// dQ tiles, heaviest first) from a global counter (tile_queue.cuh). The producer keeps streaming the next tile's operands while the epilogue
-// warps drain the accumulator, and nothing is re-initialised between tiles.
+// dQ tiles, heaviest first) from a global counter (tile_queue.cuh). The producer keeps streaming the next tile's
+// operands while the epilogue warps drain the accumulator, and nothing is re-initialised between tiles.
+//
+// Chunks. One launch covers the head units and row tiles whose P / dS planes the workspace currently holds
+// (BwdParams::c_*). A dQ tile only needs its own rows, so it is complete within its chunk. A dK / dV tile sums
+// over all rows of its sequence; when a chunk holds only part of them (carry_mode), the tile starts from the
+// fp32 accumulator the previous chunk left in `carry` (loaded into TMEM by the epilogue warps before the first
+// MMA) and leaves its own there unless it is the last. Chunks run head units ascending and row tiles
+// descending, which is the order of the contraction in a single launch, so the result is bit-identical.
 #include <cstring>
 
+#include "bwd_common.cuh"
 #include "common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -45,44 +56,51 @@ constexpr int kTileQ = kAbort + 4;  // TileQueue, kTileQueueBytes
 constexpr int kConsumers = 2 + 1 + 16;  // producers, MMA issuer, epilogue warps of both CTAs
 constexpr int kCtrlBytes = 256;
 constexpr int kSmemBytes = kOffCtrl + kCtrlBytes;
-constexpr int kThreads = 384;  // producer, MMA issuer, 2 idle warps, 8 epilogue warps
+constexpr int kThreads = 384;  // producer, MMA issuer, scheduler, 1 idle warp, 8 epilogue warps
 enum { kModeDV = 0, kModeDK = 1, kModeDQ = 2 };
 }  // namespace grad
 
 struct GradLaunch {
-  int n_kv_pairs;         // tiles producing dV / dK (even: dV, odd: dK)
-  int n_dq_pairs;         // tiles producing dQ
-  int dq_pairs_per_unit;  // packed layout: upper bound of dQ tiles per head unit; batched: per sequence
+  int n_kv_pairs;         // tile slots producing dV / dK (even: dV, odd: dK)
+  int n_dq_pairs;         // tile slots producing dQ
+  int dq_pairs_per_unit;  // packed layout: upper bound of dQ tiles per head unit
+  int kv0, kv1;           // KV heads the chunk touches
 };
 
 // One output tile of a CTA pair.
 struct GradTile {
   int mode, b, sq, sk, q_off, k_off, tile_base, n_row_tiles;
-  int kvh, kt;      // dK/dV: kv head, key tile (256 keys)
-  int hu, tp;       // dQ: head unit, tile pair
-  int n_stages, t_min, units;
+  int kvh, kt;        // dK/dV: kv head, key tile (256 keys)
+  int hu, tp;         // dQ: head unit, tile pair
+  int u_lo, u_hi;     // dK/dV: query heads of the group summed in this chunk (unfolded groups; else 0, 1)
+  int r_lo, r_hi;     // dK/dV: row tiles summed in this chunk
+  int kv_tile;        // dK/dV: index of the key tile over all sequences (slot of its travelling accumulator)
+  int carry_in, carry_out;
+  int n_stages;
 };
 
-// Decode tile `idx` of the launch. Returns false when the slot holds no tile.
+// Decode tile slot `idx` of the launch. Returns false when the slot holds no tile for this chunk.
 __device__ __forceinline__ bool grad_decode(const BwdParams& p, const GradLaunch& gl, int idx, GradTile& t) {
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
   const bool folded = g.pack_g == g.group;
-  t.q_off = 0, t.k_off = 0, t.t_min = 0, t.units = 1, t.kvh = 0, t.kt = 0, t.hu = 0, t.tp = 0, t.n_stages = 0;
+  t.q_off = 0, t.k_off = 0, t.kvh = 0, t.kt = 0, t.hu = 0, t.tp = 0, t.n_stages = 0;
+  t.u_lo = 0, t.u_hi = 1, t.r_lo = 0, t.r_hi = 0, t.kv_tile = 0, t.carry_in = 0, t.carry_out = 0;
   if (idx < gl.n_kv_pairs) {
     t.mode = idx & 1;
     int i2 = idx >> 1;
     if (g.cu_q == nullptr) {
       t.kt = i2 % p.key_tiles;  // heaviest key tile of a sequence first under a causal mask
       i2 /= p.key_tiles;
-      t.b = i2 % g.batch;
-      t.kvh = i2 / g.batch;
+      t.b = p.c_b0 + i2 % p.c_nb;
+      t.kvh = gl.kv0 + i2 / p.c_nb;
       t.sq = g.seqlen_q, t.sk = g.seqlen_k;
       t.n_row_tiles = g.row_tiles;
       t.tile_base = t.b * g.row_tiles;
+      t.kv_tile = t.b * p.key_tiles + t.kt;
     } else {
-      t.kvh = i2 / p.key_tiles;
-      const int r = i2 - t.kvh * p.key_tiles;
+      t.kvh = gl.kv0 + i2 / p.key_tiles;
+      const int r = i2 % p.key_tiles;
       int acc_k = 0, acc_r = 0;
       t.b = -1;
       for (int i = 0; i < g.batch; ++i) {
@@ -97,30 +115,52 @@ __device__ __forceinline__ bool grad_decode(const BwdParams& p, const GradLaunch
       }
       if (t.b < 0) return false;
       t.tile_base = acc_r;
+      t.kv_tile = acc_k + t.kt;
+      if (t.sk + 64 > p.ws_pitch) return false;  // reported by the tile kernel (ST_BAD_SEQLEN)
     }
-    if (t.kvh >= g.heads_kv) return false;
+    if (t.kvh >= gl.kv1) return false;
+    int t_min = 0;
     if (g.causal) {  // first row tile that can see this key tile (bottom-right aligned)
       const int x = t.kt * 256 - (t.sk - t.sq);
-      t.t_min = x > 0 ? x / ppp : 0;
+      t_min = x > 0 ? x / ppp : 0;
     }
-    t.units = folded ? 1 : g.group;
-    t.n_stages = t.units * max(t.n_row_tiles - t.t_min, 0) * 2;  // 64-row chunks
+    const int units = folded ? 1 : g.group;
+    if (!folded) {
+      t.u_lo = max(0, p.c_hu0 - t.kvh * g.group);
+      t.u_hi = min(g.group, p.c_hu1 - t.kvh * g.group);
+    }
+    int lo, hi;
+    chunk_tile_range(p, t.tile_base, lo, hi);
+    t.r_lo = max(t_min, lo);
+    t.r_hi = min(t.n_row_tiles, hi);
+    const int rows = max(t.r_hi - t.r_lo, 0), nu = max(t.u_hi - t.u_lo, 0);
+    t.n_stages = nu * rows * 2;  // 64-row chunks
+    if (t.n_row_tiles - t_min > 0) {
+      // the tile's whole sum is (query heads ascending) x (row tiles descending); this chunk holds a box of it
+      t.carry_in = (t.u_lo > 0) || (max(t_min, hi) < t.n_row_tiles);
+      t.carry_out = (t.u_hi < units) || (t_min < min(lo, t.n_row_tiles));
+      if (t.n_stages == 0) return false;  // nothing of it in this chunk: leave its accumulator alone
+    } else {
+      // no query row sees these keys: zeros, written once, by the chunk that holds the sequence's last tile pair
+      const int top = min(t.tile_base + ((max(t.n_row_tiles, 1) - 1) & ~1), p.g_end - 1);
+      if (t.u_lo > 0 || top < p.c_g0 || top >= p.c_g1) return false;
+    }
   } else {
     t.mode = grad::kModeDQ;
     int i2 = idx - gl.n_kv_pairs;
     if (i2 >= gl.n_dq_pairs) return false;
     if (g.cu_q == nullptr) {
-      t.tp = i2 % gl.dq_pairs_per_unit;
-      i2 /= gl.dq_pairs_per_unit;
-      t.b = i2 % g.batch;
-      t.hu = i2 / g.batch;
-      if (g.causal) t.tp = gl.dq_pairs_per_unit - 1 - t.tp;  // heaviest first
+      const int tl = i2 % p.c_ntp;
+      i2 /= p.c_ntp;
+      t.b = p.c_b0 + i2 % p.c_nb;
+      t.hu = p.c_hu0 + i2 / p.c_nb;
+      t.tp = p.c_tp0 + (g.causal ? p.c_ntp - 1 - tl : tl);  // heaviest first
       t.sq = g.seqlen_q, t.sk = g.seqlen_k;
       t.n_row_tiles = g.row_tiles;
       t.tile_base = t.b * g.row_tiles;
     } else {
-      t.hu = i2 / gl.dq_pairs_per_unit;
-      const int r = i2 - t.hu * gl.dq_pairs_per_unit;
+      t.hu = p.c_hu0 + i2 / gl.dq_pairs_per_unit;
+      const int r = i2 % gl.dq_pairs_per_unit;
       int acc_p = 0, acc_r = 0;
       t.b = -1;
       for (int i = 0; i < g.batch; ++i) {
@@ -138,8 +178,9 @@ __device__ __forceinline__ bool grad_decode(const BwdParams& p, const GradLaunch
       }
       if (t.b < 0) return false;
       t.tile_base = acc_r;
+      if (t.sk + 64 > p.ws_pitch) return false;
     }
-    if (t.hu >= g.head_units) return false;
+    if (t.hu >= p.c_hu1 || !chunk_has_tile(p, t.tile_base, 2 * t.tp)) return false;
     t.kvh = folded ? t.hu : t.hu / g.group;
     // key extent written for this tile pair = that of its last tile, in 256-key blocks
     const int t_last = min(2 * t.tp + 1, t.n_row_tiles - 1);
@@ -172,8 +213,8 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
   const bool folded = g.pack_g == g.group;
-  // optional cycle counters of one pair (debug[8..15]): where the MMA issuer and one epilogue warp wait
-  const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
+  // cycle counters of one pair (debug[8..15]): where the MMA issuer and one epilogue warp wait (-DSPLITD_PROFILE)
+  const bool prof = kProfile && p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -226,21 +267,22 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
           const CUtensorMap* tm_b = t.mode == kModeDK ? &tm_q : &tm_do;
           const int qb = g.cu_q ? 0 : t.b;
           const int key0 = t.kt * 256 + rank * 128;
-          for (int u = 0; u < t.units && ok; ++u) {
+          for (int u = t.u_lo; u < t.u_hi && ok; ++u) {
             const int h = folded ? t.kvh : t.kvh * g.group + u;
+            const int plane = (h - p.c_hu0) * 2 + t.mode;
             // last row tile first: under a causal mask the tiles of one KV head start at different rows, and
             // walking down from the common end keeps the pairs that run side by side on the same Q / dO rows
-            for (int rt = t.n_row_tiles - 1; rt >= t.t_min && ok; --rt) {
+            for (int rt = t.r_hi - 1; rt >= t.r_lo && ok; --rt) {
               for (int c = 0; c < 2 && ok; ++c) {
                 uint32_t st = 0, bar = 0, stage = 0;
                 acquire(st, bar, stage);
                 if (!ok) break;
-                const int ws_row = (t.tile_base + rt) * kRowsPerPair + c * kRowsPerCta;
+                const int ws_row = static_cast<int>(chunk_ws_row(p, t.tile_base, rt)) + c * kRowsPerCta;
                 const int pos = t.q_off + rt * ppp + c * g.pos_per_cta;
                 if (elect_one()) {
                   if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
-                  tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, h * 2 + t.mode);
-                  tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, h * 2 + t.mode);
+                  tma_load_3d_pair(st, &tm_ws, bar, key0, ws_row, plane);
+                  tma_load_3d_pair(st + 8192, &tm_ws, bar, key0 + 64, ws_row, plane);
 #pragma unroll
                   for (int m = 0; m < 2; ++m) {
                     const int d0 = m * 256 + rank * 128;
@@ -255,15 +297,16 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
         } else {
           const int kb = g.cu_k ? 0 : t.b;
           const int my_tile_ld = min(2 * t.tp + rank, t.n_row_tiles - 1);  // clamped when the last pair has one tile
-          const int ws_row = (t.tile_base + my_tile_ld) * kRowsPerPair;
+          const int ws_row = static_cast<int>(chunk_ws_row(p, t.tile_base, my_tile_ld));
+          const int plane = (t.hu - p.c_hu0) * 2 + 1;
           for (int c = 0; c < t.n_stages && ok; ++c) {
             uint32_t st = 0, bar = 0, stage = 0;
             acquire(st, bar, stage);
             if (!ok) break;
             if (elect_one()) {
               if (rank == 0) mbar_arrive_expect_tx(ctrl + kBarFull + 8 * stage, 2 * kStageBytes);
-              tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, t.hu * 2 + 1);
-              tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, t.hu * 2 + 1);
+              tma_load_3d_pair(st, &tm_ws, bar, c * 64, ws_row, plane);
+              tma_load_3d_pair(st + 8192, &tm_ws, bar, c * 64, ws_row + 64, plane);
 #pragma unroll
               for (int m = 0; m < 2; ++m) {
                 const int d0 = m * 256 + rank * 128;
@@ -291,15 +334,20 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
         if (idx < 0 || idx >= total_tiles) break;
         if (!grad_decode(p, gl, idx, t) || t.n_stages == 0) continue;
         const bool kv = t.mode != kModeDQ;
-        const uint32_t idesc = make_idesc(false, kv, true, 256, 256);
+        const uint32_t idesc = make_idesc(true, kv, true, 256, 256);  // fp16 x fp16 -> fp32
         const uint32_t a_step = kv ? (2048u >> 4) : (32u >> 4);  // 16 contraction elements further
         const uint32_t a_lbo = kv ? 8192u : 16u;
-        if (tiles > 0) {  // the previous tile's epilogue must have drained the accumulator
+        // The accumulator must be free: drained by the previous tile's epilogue, and (carry_mode) preloaded with
+        // what the earlier chunks summed, which the epilogue warps signal once per tile, the first included.
+        if (p.carry_mode || tiles > 0) {
           const long long t0 = prof ? clock64() : 0;
-          ok = mbar_wait<true>(ctrl + kBarAccFree, (tiles - 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA);
+          const uint32_t ph = p.carry_mode ? (tiles & 1) : ((tiles - 1) & 1);
+          ok = mbar_wait<true>(ctrl + kBarAccFree, ph, abort_flag, p.status, ST_TIMEOUT_MMA);
           ok = __all_sync(0xffffffffu, ok);
           if (prof) t_free += clock64() - t0;
+          if (ok) tc_fence_after_sync();
         }
+        const uint32_t acc0 = t.carry_in ? 1u : 0u;
         for (int c = 0; c < t.n_stages && ok; ++c) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           const long long t0 = prof ? clock64() : 0;
@@ -316,7 +364,7 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
 #pragma unroll
               for (int m = 0; m < 2; ++m)
                 umma_ss<2>(tmem_base + m * 256, desc_join(a0 + k * a_step),
-                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc, (c | k) != 0);
+                           desc_join(b0 + ((m * 16384 + k * 2048) >> 4)), idesc, (c | k) | acc0);
             }
             umma_commit_pair(ctrl + kBarEmpty + 8 * s, 3);
             if (c == t.n_stages - 1) umma_commit_pair(ctrl + kBarAccDone, 3);
@@ -337,7 +385,8 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
   } else if (warp == 2) {
     // ------------------------------------------------------------------ tile scheduler (leader CTA)
     if (rank == 0 && lane == 0)
-      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterGrad, pair_id, n_pairs, total_tiles, abort_flag, p.status);
+      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterGrad, p.tile_counters + kCounterGradDone, pair_id, n_pairs,
+                  total_tiles, abort_flag, p.status);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue: TMEM -> bf16 -> global
     // 8 warps: warp & 3 selects the 32 TMEM lanes (output rows), (warp - 4) / 4 the 256-column half.
@@ -353,6 +402,29 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
       if (idx < 0 || idx >= total_tiles) break;
       if (!grad_decode(p, gl, idx, t)) continue;
       const bool live = t.n_stages > 0;
+      // this thread's 32-column blocks of the travelling accumulator: [column block][row = TMEM lane][32 floats]
+      float* cslot = nullptr;
+      if (p.carry_mode && live && t.mode != kModeDQ)
+        cslot = carry_slot(p, t.kv_tile, t.mode, rank) + static_cast<int64_t>(half * 8) * (128 * 32) + (q * 32 + lane) * 32;
+      if (p.carry_mode && live) {
+        if (t.carry_in) {  // the sum of the earlier chunks goes back into the accumulator
+#pragma unroll 1
+          for (int cb = 0; cb < 8; ++cb) {
+            uint32_t a[32];
+            const uint4* src = reinterpret_cast<const uint4*>(cslot + static_cast<int64_t>(cb) * (128 * 32));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint4 w = src[i];
+              a[4 * i] = w.x, a[4 * i + 1] = w.y, a[4 * i + 2] = w.z, a[4 * i + 3] = w.w;
+            }
+            tmem_st32(lane_addr + cb * 32, a);
+          }
+          tmem_st_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_acc_free);  // cluster-scope release: the peer's TMEM writes
+      }
       const long long t0 = prof ? clock64() : 0;
       if (live) {
         ok = mbar_wait(ctrl + kBarAccDone, tiles & 1, abort_flag, p.status, ST_TIMEOUT_SOFTMAX);
@@ -362,9 +434,26 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
       }
       const long long t1 = prof ? clock64() : 0;
       t_done += t1 - t0;
-      // destination rows of the four rows this thread stores (chunk lane & 3 of each)
+      if (live && t.carry_out) {
+        // not the last chunk of this tile: the raw fp32 accumulator travels on
+#pragma unroll 1
+        for (int cb = 0; cb < 8; ++cb) {
+          uint32_t a[32];
+          tmem_ld32(lane_addr + cb * 32, a);
+          tmem_ld_wait();
+          uint4* dst = reinterpret_cast<uint4*>(cslot + static_cast<int64_t>(cb) * (128 * 32));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_uint4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+        }
+        tc_fence_before_sync();  // (carry_mode: the next tile's arrival above follows in program order)
+        ++tiles;
+        continue;
+      }
+      // destination rows of the four rows this thread stores (chunk lane & 3 of each), and the power of two
+      // that takes the fp16 scale of P / dS out again
       uint16_t* drow[4];
       bool store[4];
+      float unscale;
       if (t.mode != kModeDQ) {
         uint16_t* base = reinterpret_cast<uint16_t*>(t.mode == kModeDK ? p.dk : p.dv);
         const int64_t sb = t.mode == kModeDK ? p.dk_stride_b : p.dv_stride_b;
@@ -388,6 +477,10 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
           store[j] = my_tile < t.n_row_tiles && pos < t.sq;
         }
       }
+      {
+        const uint32_t* st = p.stats + static_cast<int64_t>(t.b * g.heads_kv + t.kvh) * kStatWords;
+        unscale = pow2i(t.mode == kModeDV ? -(kPShift + do_exponent(st)) : -ds_exponent(st, p.scale));
+      }
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {  // 64 accumulator columns per step
         uint32_t x[32];
@@ -398,14 +491,16 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
           tmem_ld_wait();
           if (c == 3) {  // accumulator read: the next tile's first MMA may overwrite it
             tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(leader_acc_free);
+            if (!p.carry_mode) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive_remote(leader_acc_free);
+            }
             if (prof) t_drain += clock64() - t1;
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            x[i] = pack2<false>(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
-            x[16 + i] = pack2<false>(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]));
+            x[i] = pack2<false>(__uint_as_float(a[2 * i]) * unscale, __uint_as_float(a[2 * i + 1]) * unscale);
+            x[16 + i] = pack2<false>(__uint_as_float(b[2 * i]) * unscale, __uint_as_float(b[2 * i + 1]) * unscale);
           }
           // 64 columns x 2 bytes = 4 chunks of 32 bytes of this thread's row; after the transpose the thread
           // holds chunk (lane & 3) of rows Lr .. Lr + 3, so each 256-bit store instruction of the warp writes
@@ -443,54 +538,61 @@ splitd_bwd_grad_kernel(const __grid_constant__ CUtensorMap tm_ws, const __grid_c
 }
 
 // modes: bit 0 = dK and dV, bit 1 = dQ
-int launch_bwd_grad(const splitd_params* p, cudaStream_t stream, int modes) {
+int launch_bwd_grad(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream, int modes) {
   BwdParams bp;
-  if (int e = fill_bwd_params(p, bp)) return e;
-  if (int e = check_workspace(p)) return e;
+  if (int e = fill_bwd_params(p, bp, &pl)) return e;
+  plan_chunk(pl, chunk, p, bp);
   const TileGeom& g = bp.g;
+  const int nhu = bp.c_hu1 - bp.c_hu0;
   CUtensorMap tm_ws, tm_do, tm_q, tm_k;
   {
-    const uint64_t dims[3] = {(uint64_t)bp.ws_pitch, (uint64_t)bp.ws_rows, (uint64_t)(2 * g.head_units)};
+    const uint64_t dims[3] = {(uint64_t)bp.ws_pitch, (uint64_t)bp.ws_rows, (uint64_t)(2 * nhu)};
     const int64_t strides[3] = {1, bp.ws_pitch, bp.ws_rows * bp.ws_pitch};
     const uint32_t box[3] = {64, 64, 1};
     if (int e = make_tmap(&tm_ws, bp.ws, 3, dims, strides, box, "workspace")) return e;
   }
-  if (int e = make_q_tmap(&tm_do, p->dout, p, g, p->do_strides, g.pos_per_cta, "dout")) return e;
-  if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, g.pos_per_cta, "q")) return e;
-  if (int e = make_kv_tmap(&tm_k, p->k, p, p->k_strides, 64, "k")) return e;
   const bool varlen = p->cu_seqlens_q != nullptr;
+  {  // the fp16 copies are contiguous (B,S,H,512) / (T,H,512)
+    const int64_t sq = varlen ? p->total_q : p->seqlen_q, sk = varlen ? p->total_k : p->seqlen_k;
+    const int64_t qs[3] = {sq * p->heads_q * kHeadDim, static_cast<int64_t>(p->heads_q) * kHeadDim, kHeadDim};
+    const int64_t ks[3] = {sk * p->heads_kv * kHeadDim, static_cast<int64_t>(p->heads_kv) * kHeadDim, kHeadDim};
+    if (int e = make_q_tmap(&tm_do, bp.do_h, p, g, qs, g.pos_per_cta, "dout (fp16 copy)")) return e;
+    if (int e = make_q_tmap(&tm_q, bp.q_h, p, g, qs, g.pos_per_cta, "q (fp16 copy)")) return e;
+    if (int e = make_kv_tmap(&tm_k, bp.k_h, p, ks, 64, "k (fp16 copy)")) return e;
+  }
+  const bool folded = g.pack_g == g.group;
   GradLaunch gl;
-  gl.n_kv_pairs = 0;
-  gl.n_dq_pairs = 0;
+  gl.kv0 = folded ? bp.c_hu0 : bp.c_hu0 / g.group;
+  gl.kv1 = folded ? bp.c_hu1 : (bp.c_hu1 - 1) / g.group + 1;
   gl.dq_pairs_per_unit = varlen ? (g.row_tiles + g.batch + 1) / 2 : (g.row_tiles + 1) / 2;
-  long long kv = 2ll * bp.key_tiles * g.heads_kv * (varlen ? 1 : g.batch);
-  long long dq = static_cast<long long>(gl.dq_pairs_per_unit) * g.head_units * (varlen ? 1 : g.batch);
+  long long kv = 2ll * bp.key_tiles * (gl.kv1 - gl.kv0) * (varlen ? 1 : bp.c_nb);
+  long long dq = varlen ? static_cast<long long>(gl.dq_pairs_per_unit) * nhu : static_cast<long long>(bp.c_ntp) * bp.c_nb * nhu;
   if (!(modes & 1)) kv = 0;
   if (!(modes & 2)) dq = 0;
+  if ((modes & 3) != 3 && pl.n_chunks > 1)
+    return fail(SPLITD_ERR_WORKSPACE, "dq and dk/dv as separate steps need the whole problem in one chunk");
   const long long pairs = kv + dq;
   if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "gradient GEMM grid out of range");
   gl.n_kv_pairs = static_cast<int>(kv);
   gl.n_dq_pairs = static_cast<int>(dq);
-  cudaError_t ce =
-      cudaFuncSetAttribute(splitd_bwd_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, grad::kSmemBytes);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(grad): %s", cudaGetErrorString(ce));
   // persistent: as many CTA pairs as the device keeps resident at once
-  static int cache[64] = {};
+  static std::atomic<int> cache[64];
   const int resident = resident_cluster_pairs(splitd_bwd_grad_kernel, grad::kThreads, grad::kSmemBytes, cache);
+  if (resident <= 0) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(gradient GEMM kernel) failed");
   const long long grid_pairs = pairs < resident ? pairs : resident;
-  ce = cudaMemsetAsync(bp.tile_counters + kCounterGrad, 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
   splitd_bwd_grad_kernel<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(grad::kThreads), grad::kSmemBytes,
                            stream>>>(tm_ws, tm_do, tm_q, tm_k, bp, gl);
-  ce = cudaGetLastError();
+  cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "gradient GEMM launch failed: %s", cudaGetErrorString(ce));
   return 0;
 }
 
-int launch_bwd_dq(const splitd_params* p, cudaStream_t stream) {
-  if (int e = launch_bwd_pds(p, stream)) return e;
-  return launch_bwd_grad(p, stream, 2);
+int launch_bwd_chunk(const splitd_params* p, const BwdPlan& pl, int chunk, int stages, cudaStream_t stream) {
+  if (stages & 1)
+    if (int e = launch_bwd_pds(p, pl, chunk, stream)) return e;
+  const int modes = ((stages & 2) ? 1 : 0) | ((stages & 4) ? 2 : 0);
+  if (modes) return launch_bwd_grad(p, pl, chunk, stream, modes);
+  return 0;
 }
-int launch_bwd_dkdv(const splitd_params* p, cudaStream_t stream) { return launch_bwd_grad(p, stream, 1); }
 
 }  // namespace sd

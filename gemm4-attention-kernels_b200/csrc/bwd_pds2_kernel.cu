@@ -1,12 +1,14 @@
-// Backward step 2a, two-pass form: P and dS come from two GEMM passes that alternate inside one kernel.
+// Backward step 2a: the P and dS tiles, from two GEMM passes that alternate inside one kernel.
 //     pass 0:  S  = Q K^T      ->  P  = exp2(S*scale*log2e - lse_log2)          (written to the workspace)
 //     pass 1:  dP = dO V^T     ->  dS = P * (dP - dpsum) * scale                (P read back, dS written)
 // (the math of src/fmha_dq_sm90_d512.py:1040-1090 / src/fmha_dkdv_sm90_d512.py:1060-1130 of the reference).
+// Both are stored as fp16 with power-of-two scales (bwd_common.cuh): three more significant bits than bf16 at
+// the same bytes, which is what keeps dQ and dK within twice the error of a result that is rounded once.
 //
 // Why two passes: with ONE resident A operand (Q or dO) a CTA can hold 128 rows of it (128 KB), so every MMA
 // is a cta_group::2 UMMA with M = 256 (128 rows per CTA, TMEM lane = row), N = 256 keys: 128 cycles per
-// MMA for 4 KB of streamed B operand per CTA instead of 64 cycles, i.e. half the K/V bytes per FLOP of the
-// one-pass kernel (bwd_pds_kernel.cu), whose speed is set by that stream.
+// MMA for 4 KB of streamed B operand per CTA instead of 64 cycles, i.e. half the K/V bytes per FLOP of a
+// kernel that does both GEMMs per key step with 64 rows per CTA (measured 6 % slower on this step).
 // Why they alternate: a pair runs pass 0 over a chunk of kChunkSteps key steps and then pass 1 over the same
 // chunk, so the P values pass 1 reads (<= 0.5 MB per pair) are still in L2 and HBM sees each tile element twice
 // (P out, dS out) like in the one-pass kernel. The resident operand is swapped at every pass switch, block by
@@ -17,9 +19,12 @@
 // the even tile come out as zeros, which is what the gradient GEMMs expect.
 // Shared memory: A resident (128 x 512 bf16 = 128 KB in eight 64-column blocks), B ring 6 x 16 KB. TMEM: two
 // 256-column buffers. Persistent pairs drawing tiles from a work counter (tile_queue.cuh); whole-warp issue
-// loops with an elected lane (see bwd_pds_kernel.cu for the measurements behind both).
+// loops with an elected lane (a stage loop run by one lane under a divergent branch costs twice the cycles).
+// One launch covers one chunk of the problem (BwdParams::c_*): the head units and row tiles whose planes the
+// workspace currently holds.
 #include <cstring>
 
+#include "bwd_common.cuh"
 #include "common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -60,24 +65,24 @@ struct PairTile {
   int n_steps;
 };
 
-// Tile pair `idx` of the launch (heaviest first under a causal mask). `ppu`: tile pairs per head unit
-// (packed layout: an upper bound over all sequences; batched: per sequence).
+// Tile pair `idx` of the launch (heaviest first under a causal mask). `ppu`: tile pairs per head unit over all
+// sequences of the packed layout (an upper bound). Returns false for a slot without a tile of this chunk.
 __device__ __forceinline__ bool pds2_decode(const BwdParams& p, int ppu, int idx, PairTile& t) {
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;  // positions per 128-row tile
   t.q_off = 0, t.k_off = 0;
   if (g.cu_q == nullptr) {
-    t.tp = idx % ppu;
-    idx /= ppu;
-    t.b = idx % g.batch;
-    t.hu = idx / g.batch;
+    const int tl = idx % p.c_ntp;
+    idx /= p.c_ntp;
+    t.b = p.c_b0 + idx % p.c_nb;
+    t.hu = p.c_hu0 + idx / p.c_nb;
+    t.tp = p.c_tp0 + (g.causal ? p.c_ntp - 1 - tl : tl);
     t.sq = g.seqlen_q, t.sk = g.seqlen_k;
     t.n_row_tiles = g.row_tiles;
     t.tile_base = t.b * g.row_tiles;
-    if (g.causal) t.tp = ppu - 1 - t.tp;
   } else {
-    t.hu = idx / ppu;
-    const int r = idx - t.hu * ppu;
+    t.hu = p.c_hu0 + idx / ppu;
+    const int r = idx % ppu;
     int acc_p = 0, acc_r = 0;
     t.b = -1;
     for (int i = 0; i < g.batch; ++i) {
@@ -95,8 +100,12 @@ __device__ __forceinline__ bool pds2_decode(const BwdParams& p, int ppu, int idx
     }
     if (t.b < 0) return false;
     t.tile_base = acc_r;
+    if (t.sk + 64 > p.ws_pitch) {  // the caller's max_seqlen_k was too small for this sequence: no row to write to
+      if (p.status) atomicCAS(p.status, 0, ST_BAD_SEQLEN);
+      return false;
+    }
   }
-  if (t.hu >= g.head_units) return false;
+  if (t.hu >= p.c_hu1 || !chunk_has_tile(p, t.tile_base, 2 * t.tp)) return false;
   t.hkv = (g.pack_g == g.group) ? t.hu : t.hu / g.group;
   const int t_last = min(2 * t.tp + 1, t.n_row_tiles - 1);
   int kv_hi = t.sk;
@@ -134,8 +143,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const TileGeom& g = p.g;
   const int ppp = 2 * g.pos_per_cta;
 
-  // optional cycle counters of one pair (debug[0..5]), summed over its tiles
-  const bool prof = p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
+  // cycle counters of one pair (debug[0..7]), summed over its tiles; compiled in with -DSPLITD_PROFILE only
+  const bool prof = kProfile && p.debug != nullptr && pair_id == (n_pairs >> 1) && rank == 0;
   float* dbg = p.debug;
   long long t_a = 0, t_b = 0, t_c = 0, t_m0 = 0, t_m1 = 0;
 
@@ -287,7 +296,8 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else if (warp == 3) {
     if (rank == 0 && lane == 0)
-      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterPds, pair_id, n_pairs, total_tiles, abort_flag, p.status);
+      tq_schedule(ctrl + kTileQ, p.tile_counters + kCounterPds, p.tile_counters + kCounterPdsDone, pair_id, n_pairs,
+                  total_tiles, abort_flag, p.status);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ element-wise warps
     // TMEM lane = row of the tile; warp & 3 selects the 32 lanes, (warp - 4) / 4 the 128-key half of the step.
@@ -314,25 +324,30 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       int limit = t.sk - 1;
       if (g.causal) limit = min(limit, pos + t.sk - t.sq);
       if (!row_ok) limit = -1;
-      float lse2 = 0.f, nds = 0.f;  // lse_log2 of the row (pass 0); -dpsum * scale (pass 1)
+      // pass 0 stores P * 2^14, pass 1 stores dS * 2^e (bwd_common.cuh); both factors are folded into constants:
+      //   P'  = exp2(S * scale_log2 - (lse_log2 - 14))
+      //   t'  = (dP - dpsum) * scale * 2^(e - 14)  (fp16),   dS' = P' * t'  (one packed fp16 multiply)
+      float lse2 = 0.f, t_mul = 0.f, t_add = 0.f;
       if (row_ok) {
         const int64_t ridx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + t.q_off + pos
                                     : (static_cast<int64_t>(t.b) * g.heads_q + head) * t.sq + pos;
-        lse2 = p.lse_log2[ridx];
-        nds = -p.dpsum[ridx] * p.scale;
+        const int e = ds_exponent(p.stats + static_cast<int64_t>(t.b * g.heads_kv + t.hkv) * kStatWords, p.scale);
+        lse2 = p.lse_log2[ridx] - static_cast<float>(kPShift);
+        t_mul = p.scale * pow2i(e - kPShift);
+        t_add = -p.dpsum[ridx] * t_mul;
       }
       // this thread's row in the P plane; the dS plane is `plane` elements further
-      uint16_t* ws_row = p.ws + (static_cast<int64_t>(t.hu) * 2) * plane +
-                         (static_cast<int64_t>(t.tile_base + min(rt, t.n_row_tiles - 1)) * kRowsPerPair + L) * p.ws_pitch;
+      uint16_t* ws_row = p.ws + (static_cast<int64_t>(t.hu - p.c_hu0) * 2) * plane +
+                         (chunk_ws_row(p, t.tile_base, min(rt, t.n_row_tiles - 1)) + L) * p.ws_pitch;
       // after the 4 x 4 chunk transposes a thread handles chunk (lane & 3) of rows (lane & ~3) + r, r = 0..3
       const int64_t row_delta0 = static_cast<int64_t>((lane & ~3) - lane) * p.ws_pitch;
 
       // pass 1: the P values of a step come back with the access pattern of the stores (lane l reads 32-byte
       // chunk l & 3 of rows (l & ~3) + r: whole 128-byte lines per instruction, a quarter of the L1 wavefronts
-      // of own-row loads) and the same 4 x 4 transposes, which are their own inverse, put every thread's own row
-      // back together right before use. The values were stored by lanes of this same warp a chunk of steps ago
-      // (__syncwarp orders the two) and normally still sit in L2. Each 64-key half is re-loaded for the NEXT
-      // step as soon as this step is done with it, so the latency of the loads hides behind the rest of the step.
+      // of own-row loads) and are used in that layout. The values were stored by lanes of this same warp a chunk
+      // of steps ago (__syncwarp orders the two) and normally still sit in L2. Each 64-key half is re-loaded for
+      // the NEXT step as soon as this step is done with it, so the latency of the loads hides behind the rest of
+      // the step.
       uint32_t pq[64];
       auto load_p_half = [&](int step, int h2) {
         const uint16_t* src = ws_row + row_delta0 + step * kStepKeys + ch * 128 + h2 * 64 + (lane & 3) * 16;
@@ -383,42 +398,43 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (full) {
 #pragma unroll
                   for (int i = 0; i < 64; i += 2)
-                    x[i >> 1] = pack2<false>(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2)),
-                                             ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2)));
+                    x[i >> 1] = pack_half2(ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2)),
+                                           ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2)));
                 } else {
 #pragma unroll
                   for (int i = 0; i < 64; i += 2) {
                     const float a = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, -lse2));
                     const float bb = ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -lse2));
-                    x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+                    x[i >> 1] = pack_half2(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
                   }
                 }
+                transpose_chunks32_4x4(x, lane);
               } else {
-                uint32_t(&pw)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pq[h2 * 32]);
-                transpose_chunks32_4x4(pw, lane);  // back to this thread's own row
+                // t' of this thread's own row, packed to fp16, goes through the SAME 4 x 4 chunk transpose as the
+                // stores; P' was loaded in that layout already, so dS' is one packed multiply per register and
+                // nothing has to be transposed back.
                 if (full) {
 #pragma unroll
-                  for (int i = 0; i < 64; i += 2) {
-                    const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
-                    x[i >> 1] = pack2<false>(p0 * fmaf(__uint_as_float(s[i]), p.scale, nds),
-                                             p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, nds));
-                  }
+                  for (int i = 0; i < 64; i += 2)
+                    x[i >> 1] = pack_half2(fmaf(__uint_as_float(s[i]), t_mul, t_add),
+                                           fmaf(__uint_as_float(s[i + 1]), t_mul, t_add));
                 } else {
-                  // P is already 0 where masked; the select only guards against non-finite dP of rows / keys
-                  // outside the sequence
+                  // masked entries: P' is 0 there already; t' = 0 guards against non-finite dP of rows / keys
+                  // outside the sequence (0 * inf)
 #pragma unroll
                   for (int i = 0; i < 64; i += 2) {
-                    const float p0 = __uint_as_float(pw[i >> 1] << 16), p1 = __uint_as_float(pw[i >> 1] & 0xffff0000u);
-                    const float a = p0 * fmaf(__uint_as_float(s[i]), p.scale, nds);
-                    const float bb = p1 * fmaf(__uint_as_float(s[i + 1]), p.scale, nds);
-                    x[i >> 1] = pack2<false>(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
+                    const float a = fmaf(__uint_as_float(s[i]), t_mul, t_add);
+                    const float bb = fmaf(__uint_as_float(s[i + 1]), t_mul, t_add);
+                    x[i >> 1] = pack_half2(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
                   }
                 }
+                transpose_chunks32_4x4(x, lane);
+#pragma unroll
+                for (int w = 0; w < 32; ++w) x[w] = mul_half2(x[w], pq[h2 * 32 + w]);
                 if (j + 1 < c1) load_p_half(j + 1, h2);  // these registers are free again: next step's P
               }
               // 64 keys x 2 bytes = 4 chunks of 32 bytes per row; after the transpose every 256-bit store
               // instruction of the warp writes whole 128-byte lines
-              transpose_chunks32_4x4(x, lane);
               if (tile_valid) {
                 uint16_t* dst = ws_row + (mode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
 #pragma unroll
@@ -451,10 +467,10 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   }
 }
 
-int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream) {
+int launch_bwd_pds(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream) {
   BwdParams bp;
-  if (int e = fill_bwd_params(p, bp)) return e;
-  if (int e = check_workspace(p)) return e;
+  if (int e = fill_bwd_params(p, bp, &pl)) return e;
+  plan_chunk(pl, chunk, p, bp);
   const TileGeom& g = bp.g;
   CUtensorMap tm_q, tm_do, tm_k, tm_v;
   if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, 2 * g.pos_per_cta, "q")) return e;
@@ -463,19 +479,16 @@ int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream) {
   if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 128, "v")) return e;
   const bool varlen = p->cu_seqlens_q != nullptr;
   const int ppu = varlen ? (g.row_tiles + g.batch + 1) / 2 : (g.row_tiles + 1) / 2;
-  const long long pairs = static_cast<long long>(ppu) * g.head_units * (varlen ? 1 : g.batch);
+  const long long nhu = bp.c_hu1 - bp.c_hu0;
+  const long long pairs = varlen ? static_cast<long long>(ppu) * nhu : static_cast<long long>(bp.c_ntp) * bp.c_nb * nhu;
   if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "P/dS grid out of range");
-  cudaError_t ce =
-      cudaFuncSetAttribute(splitd_bwd_pds2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pds2::kSmemBytes);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(pds2): %s", cudaGetErrorString(ce));
-  static int cache[64] = {};
+  static std::atomic<int> cache[64];
   const int resident = resident_cluster_pairs(splitd_bwd_pds2_kernel, pds2::kThreads, pds2::kSmemBytes, cache);
+  if (resident <= 0) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(P/dS kernel) failed");
   const long long grid_pairs = pairs < resident ? pairs : resident;
-  ce = cudaMemsetAsync(bp.tile_counters + kCounterPds, 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(ce));
   splitd_bwd_pds2_kernel<<<dim3(static_cast<unsigned>(2 * grid_pairs)), dim3(pds2::kThreads), pds2::kSmemBytes,
                            stream>>>(tm_q, tm_do, tm_k, tm_v, bp, static_cast<int>(pairs), ppu);
-  ce = cudaGetLastError();
+  cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "P/dS launch failed: %s", cudaGetErrorString(ce));
   return 0;
 }

@@ -5,6 +5,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <atomic>
+
 #include "../../include/splitd_attn.h"
 #include "common.cuh"
 #include "launch.cuh"
@@ -21,15 +23,18 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+void clear_error() { g_err[0] = 0; }
+
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (fn) return fn;
+  static std::atomic<PFN_cuTensorMapEncodeTiled_v12000> cached{nullptr};
+  if (auto fn = cached.load(std::memory_order_acquire)) return fn;
   void* ptr = nullptr;
   cudaDriverEntryPointQueryResult qres;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
       qres != cudaDriverEntryPointSuccess)
     return nullptr;
-  fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  auto fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  cached.store(fn, std::memory_order_release);
   return fn;
 }
 
@@ -175,47 +180,86 @@ int splitd_fwd(const splitd_params* p, void* stream) {
 
 size_t splitd_bwd_rowstat_elems(const splitd_params* p) { return p ? bwd_rowstat_elems(p) : 0; }
 size_t splitd_bwd_workspace_bytes(const splitd_params* p) { return p ? bwd_workspace_bytes(p) : 0; }
+size_t splitd_bwd_workspace_bytes_limit(const splitd_params* p, size_t tile_bytes_limit) {
+  return p ? bwd_workspace_bytes_for(p, tile_bytes_limit) : 0;
+}
 
-int splitd_bwd_preprocess(const splitd_params* p, void* stream) {
+static int check_bwd(const splitd_params* p) {
   g_err[0] = 0;
   if (int e = check_common(p, true)) return e;
-  if (int e = check_device()) return e;
+  return check_device();
+}
+// the steps that hand P / dS from one call to the next need all of them in the workspace at once
+static int plan_single_chunk(const splitd_params* p, BwdPlan& pl, const char* what) {
+  if (int e = plan_bwd(p, pl)) return e;
+  if (pl.n_chunks != 1)
+    return fail(SPLITD_ERR_WORKSPACE,
+                "%s keeps the P/dS tiles of the whole problem in the workspace: %zu bytes required, got %zu "
+                "(splitd_bwd and splitd_bwd_chunk work with less)",
+                what, bwd_workspace_bytes_full(p), p->workspace_bytes);
+  return 0;
+}
+
+int splitd_bwd_preprocess(const splitd_params* p, void* stream) {
+  if (int e = check_bwd(p)) return e;
   return launch_bwd_preprocess(p, static_cast<cudaStream_t>(stream));
 }
 
 int splitd_bwd_dq(const splitd_params* p, void* stream) {
-  g_err[0] = 0;
-  if (int e = check_common(p, true)) return e;
-  if (int e = check_device()) return e;
-  return launch_bwd_dq(p, static_cast<cudaStream_t>(stream));
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_single_chunk(p, pl, "splitd_bwd_dq")) return e;
+  return launch_bwd_chunk(p, pl, 0, 1 | 4, static_cast<cudaStream_t>(stream));
 }
 
 int splitd_bwd_dkdv(const splitd_params* p, void* stream) {
-  g_err[0] = 0;
-  if (int e = check_common(p, true)) return e;
-  if (int e = check_device()) return e;
-  return launch_bwd_dkdv(p, static_cast<cudaStream_t>(stream));
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_single_chunk(p, pl, "splitd_bwd_dkdv")) return e;
+  return launch_bwd_chunk(p, pl, 0, 2, static_cast<cudaStream_t>(stream));
 }
 
 int splitd_bwd_tiles(const splitd_params* p, void* stream) {
-  g_err[0] = 0;
-  if (int e = check_common(p, true)) return e;
-  if (int e = check_device()) return e;
-  return launch_bwd_pds(p, static_cast<cudaStream_t>(stream));
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_single_chunk(p, pl, "splitd_bwd_tiles")) return e;
+  return launch_bwd_chunk(p, pl, 0, 1, static_cast<cudaStream_t>(stream));
 }
 
 int splitd_bwd_grads(const splitd_params* p, void* stream) {
-  g_err[0] = 0;
-  if (int e = check_common(p, true)) return e;
-  if (int e = check_device()) return e;
-  return launch_bwd_grad(p, static_cast<cudaStream_t>(stream), 3);
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_single_chunk(p, pl, "splitd_bwd_grads")) return e;
+  return launch_bwd_chunk(p, pl, 0, 2 | 4, static_cast<cudaStream_t>(stream));
+}
+
+int splitd_bwd_num_chunks(const splitd_params* p) {
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_bwd(p, pl)) return e;
+  return pl.n_chunks;
+}
+
+int splitd_bwd_chunk(const splitd_params* p, int chunk, int stages, void* stream) {
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_bwd(p, pl)) return e;
+  if (chunk < 0 || chunk >= pl.n_chunks) return fail(SPLITD_ERR_INVALID_ARGUMENT, "chunk %d of %d", chunk, pl.n_chunks);
+  if (stages != 1 && stages != 2 && stages != 3)
+    return fail(SPLITD_ERR_INVALID_ARGUMENT, "stages must be 1 (tiles), 2 (gradients) or 3 (both)");
+  return launch_bwd_chunk(p, pl, chunk, (stages & 1) | ((stages & 2) ? 6 : 0), static_cast<cudaStream_t>(stream));
 }
 
 int splitd_bwd(const splitd_params* p, void* stream) {
-  if (int e = splitd_bwd_preprocess(p, stream)) return e;
-  // P/dS tiles, then dQ, dK and dV as one GEMM launch (better tail behaviour than two launches)
-  if (int e = launch_bwd_pds(p, static_cast<cudaStream_t>(stream))) return e;
-  return launch_bwd_grad(p, static_cast<cudaStream_t>(stream), 3);
+  if (int e = check_bwd(p)) return e;
+  BwdPlan pl;
+  if (int e = plan_bwd(p, pl)) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int e = launch_bwd_preprocess(p, s)) return e;
+  // per chunk: P/dS tiles, then dQ, dK and dV as one GEMM launch (better tail behaviour than two launches)
+  for (int i = 0; i < pl.n_chunks; ++i)
+    if (int e = launch_bwd_chunk(p, pl, i, 7, s)) return e;
+  return 0;
 }
 
 }  // extern "C"

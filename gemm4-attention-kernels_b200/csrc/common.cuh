@@ -12,6 +12,12 @@ constexpr int kRowsPerPair = 2 * kRowsPerCta;
 constexpr int kChunkElems = 64;          // one 128-byte swizzle span of bf16/fp16
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+// In-kernel cycle counters (written to splitd_params::debug) exist only in builds made with -DSPLITD_PROFILE.
+#ifdef SPLITD_PROFILE
+constexpr bool kProfile = true;
+#else
+constexpr bool kProfile = false;
+#endif
 
 // Query rows are "packed": for a KV head with G query heads, row r of a tile is
 // (position r / G, query head r % G), so one tile of 128 rows shares one K/V stream
@@ -45,8 +51,20 @@ struct FwdParams {
   float* debug;
 };
 
-// Backward workspace: per head unit two bf16 matrices (P, then dS) of ws_rows x ws_pitch, rows in
-// packed order (row tile * 128 + row in tile), keys of the row's own sequence along the pitch.
+// Backward scratch ("workspace", one caller-provided buffer):
+//   [0, kWsCounterBytes)           work counters of the persistent kernels
+//   [kWsCounterBytes, + stats)     per (batch or packed sequence, KV head): kStatWords 32-bit words, the bit patterns of
+//                                  max |dO row|^2, max |V row|^2 and max |dpsum| (they bound |dS|, see ds_exponent)
+//   [dO_h, Q_h, K_h)               fp16 copies of dO (times 2^A, A per group), Q and K, contiguous (B,S,H,512) /
+//                                  (T,H,512): the B operands of the gradient GEMMs, whose A operands (P, dS) are
+//                                  fp16 (the two operands of one MMA must have the same format)
+//   [carry)                        fp32 dK / dV accumulators that travel between chunks (only when one KV head's
+//                                  rows do not fit the workspace at once)
+//   [planes)                       per head unit of the CURRENT CHUNK two fp16 matrices (P * 2^14, then dS * 2^e) of
+//                                  ws_rows x ws_pitch, rows in packed order (row tile * 128 + row in tile), keys of
+//                                  the row's own sequence along the pitch.
+// A chunk is a box (head units [c_hu0, c_hu1)) x (row tiles [c_g0, c_g1)); a row tile belongs to the chunk of the
+// FIRST tile of its (even, odd) tile pair, counted over all sequences of a head unit.
 struct BwdParams {
   TileGeom g;
   const float* lse;       // forward LSE (natural log)
@@ -55,26 +73,46 @@ struct BwdParams {
   float* lse_log2;        // lse * log2(e), same indexing as lse
   const void* o;
   const void* dout;
+  const void* q;
+  const void* k;
+  const void* v;
+  uint16_t* do_h;         // fp16 copies (see above)
+  uint16_t* q_h;
+  uint16_t* k_h;
   void* dq;
   void* dk;
   void* dv;
   int64_t o_stride_b, o_stride_s, o_stride_h;
   int64_t do_stride_b, do_stride_s, do_stride_h;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_s, v_stride_h;
   int64_t dq_stride_b, dq_stride_s, dq_stride_h;
   int64_t dk_stride_b, dk_stride_s, dk_stride_h;
   int64_t dv_stride_b, dv_stride_s, dv_stride_h;
-  uint16_t* ws;           // workspace base
-  int64_t ws_rows;        // rows per head unit (total row tiles * 128)
+  uint16_t* ws;           // planes of the current chunk
+  int64_t ws_rows;        // rows per head unit in the current chunk
   int64_t ws_pitch;       // elements per row (max sequence length rounded up to 256, plus 64 of padding)
   int total_q, total_k;
   int key_tiles;          // batched: key tiles (256 keys) per sequence; packed: upper bound over all
   float scale_log2, scale;
   int* status;
   float* debug;           // optional per-role cycle counters (tests / tuning only)
-  int* tile_counters;     // kWsCounterBytes at the end of the workspace: work counters of the persistent kernels
+  int* tile_counters;     // kWsCounterBytes at the start of the workspace
+  uint32_t* stats;        // kStatWords words per (batch, KV head)
+  float* carry;           // fp32 dK / dV accumulators between chunks (nullptr when no chunk splits a KV head)
+  int g_end;              // row tiles per head unit (packed layout: upper bound)
+  int c_hu0, c_hu1;       // chunk: head units
+  int c_g0, c_g1;         // chunk: row tiles (see above)
+  int c_b0, c_nb;         // batched layout: first batch / number of batches the chunk touches
+  int c_tp0, c_ntp;       // batched layout: first tile pair of a sequence / number of them the chunk can touch
+  int carry_mode;         // 1: dK / dV tiles may be partial in this chunk (accumulators come from / go to `carry`)
 };
 constexpr int kWsCounterBytes = 256;
-constexpr int kCounterPds = 0, kCounterGrad = 32;  // int offsets, 128 bytes apart
+constexpr int kCounterPds = 0, kCounterPdsDone = 8, kCounterGrad = 32, kCounterGradDone = 40;  // int offsets
+constexpr int kStatWords = 4;
+constexpr int kStatDo2 = 0, kStatV2 = 1, kStatDelta = 2, kStatDoMax = 3;  // kStatDoMax: max |element of dO|
+constexpr int kPShift = 14;  // P is stored as P * 2^14 in fp16: P down to 2^-28 keeps all 11 significant bits
 
 // Which tile does this CTA pair work on. Returns false when the pair has nothing to do.
 struct TileCoord {

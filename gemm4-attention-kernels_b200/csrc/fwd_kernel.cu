@@ -156,8 +156,8 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const TileGeom& g = p.g;
 
-  // optional per-role cycle counters of pair 0 (tests / tuning only), written to debug[32..51]
-  const bool prof = p.debug != nullptr && pair_id == 0 && rank == 0;
+  // per-role cycle counters of pair 0, written to debug[32..51]; compiled in with -DSPLITD_PROFILE only
+  const bool prof = kProfile && p.debug != nullptr && pair_id == 0 && rank == 0;
   long long t_a = 0, t_b = 0, t_c = 0, t_all = 0;
 
   // ---------------------------------------------------------------- setup (once per pair)
@@ -317,7 +317,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t tiles = 0;  // tiles with work done so far
       uint32_t rs = 0x3210u, qs = 0x54u;  // same slot tables as the producer's
       bool ok = true;
-      t_all = p.debug != nullptr ? clock64() : 0;
+      t_all = kProfile && p.debug != nullptr ? clock64() : 0;
       // wait on a barrier with all lanes, keep the outcome warp-uniform
       auto wait_all = [&](uint32_t bar, uint32_t parity, bool cluster_scope) {
         bool w = cluster_scope ? mbar_wait<true>(bar, parity, abort_flag, p.status, ST_TIMEOUT_MMA)
@@ -428,7 +428,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         have = has_next;
       }
       // longest-running pair of the launch in units of 1024 cycles, as an integer in debug[35]
-      if (p.debug != nullptr && lane == 0)
+      if (kProfile && p.debug != nullptr && lane == 0)
         atomicMax(reinterpret_cast<int*>(p.debug + 35), static_cast<int>((clock64() - t_all) >> 10));
       if (prof && lane == 0) {
         p.debug[34] = static_cast<float>(gs);
@@ -755,39 +755,13 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   if (pairs <= 0 || pairs > (1ll << 30)) return fail(SPLITD_ERR_INVALID_ARGUMENT, "forward grid out of range");
   fp.total_pairs = static_cast<int>(pairs);
   auto kern = p->dtype == SPLITD_DTYPE_FP16 ? splitd_fwd_kernel<true> : splitd_fwd_kernel<false>;
-  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::kSmemBytes);
-  if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(ce));
   // persistent grid: as many CTA pairs as the device can keep resident at once
-  int dev = 0, resident = 0;
-  cudaGetDevice(&dev);
-  static int cached_pairs[64][2] = {};
-  const int dt = p->dtype == SPLITD_DTYPE_FP16 ? 1 : 0;
-  if (dev >= 0 && dev < 64 && cached_pairs[dev][dt] > 0) {
-    resident = cached_pairs[dev][dt];
-  } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2);
-    cfg.blockDim = dim3(384);
-    cfg.dynamicSmemBytes = fwd::kSmemBytes;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    ce = cudaOccupancyMaxActiveClusters(&resident, kern, &cfg);
-    if (ce != cudaSuccess || resident <= 0) {
-      cudaGetLastError();
-      int sms = 0;
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      resident = sms > 1 ? sms / 2 : 1;
-    }
-    if (dev >= 0 && dev < 64) cached_pairs[dev][dt] = resident;
-  }
+  static std::atomic<int> cache[2][64];
+  const int resident = resident_cluster_pairs(kern, 384, fwd::kSmemBytes, cache[p->dtype == SPLITD_DTYPE_FP16 ? 1 : 0]);
+  if (resident <= 0) return fail(SPLITD_ERR_CUDA, "cudaFuncSetAttribute(forward kernel) failed");
   const long long launch_pairs = pairs < resident ? pairs : resident;
   kern<<<dim3(static_cast<unsigned>(2 * launch_pairs)), dim3(384), fwd::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, fp);
-  ce = cudaGetLastError();
+  cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return fail(SPLITD_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(ce));
   return 0;
 }

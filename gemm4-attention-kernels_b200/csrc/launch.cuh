@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include <atomic>
+
 #include "../../include/splitd_attn.h"
 #include "common.cuh"
 
@@ -19,25 +21,59 @@ int make_q_tmap(CUtensorMap* map, const void* base, const splitd_params* p, cons
 int make_kv_tmap(CUtensorMap* map, const void* base, const splitd_params* p, const int64_t* st, int box_rows,
                  const char* what);
 
+// How the backward cuts its (head unit) x (row tile) space into chunks whose P / dS planes fit the workspace.
+struct BwdPlan {
+  size_t head_bytes;   // work counters + per-group maxima
+  size_t copy_q_bytes, copy_k_bytes;  // fp16 copies: dO and Q (each copy_q_bytes), K
+  size_t fixed_bytes;  // head + the three copies: everything in front of the accumulators and the planes
+  size_t carry_bytes;  // fp32 dK / dV accumulators between chunks (used by mode 3 only)
+  size_t tile_bytes;   // both planes of one 128-row tile
+  size_t full_bytes;   // planes of the whole problem
+  int64_t g_end;       // row tiles per head unit (packed layout: upper bound over all sequences)
+  int64_t pitch;       // elements per plane row
+  int head_units, upk; // upk: head units per KV head (1 when the query heads fold into the rows)
+  int row_tiles_seq;   // batched layout: row tiles per sequence; 0 = packed
+  int batch;
+  int mode;            // 0 one chunk; 1 whole KV heads; 2 one KV head x some batches; 3 one head unit x a row range
+  int n_chunks, kv_per_chunk, batches_per_chunk, slices, use_carry;
+  int64_t tiles_per_chunk;
+};
+// planes of at most this many bytes by default (splitd_bwd_workspace_bytes); the caller may give more or less
+constexpr size_t kDefaultPlaneLimit = static_cast<size_t>(6) << 30;
+
 int launch_fwd(const splitd_params* p, cudaStream_t stream);
 int launch_bwd_preprocess(const splitd_params* p, cudaStream_t stream);
-int launch_bwd_pds(const splitd_params* p, cudaStream_t stream);
-int launch_bwd_pds_two_pass(const splitd_params* p, cudaStream_t stream);
-int launch_bwd_grad(const splitd_params* p, cudaStream_t stream, int modes);
-int launch_bwd_dq(const splitd_params* p, cudaStream_t stream);
-int launch_bwd_dkdv(const splitd_params* p, cudaStream_t stream);
+// stages: bit 0 = P / dS tiles of chunk `chunk`, bit 1 = dK and dV, bit 2 = dQ from them
+int launch_bwd_chunk(const splitd_params* p, const BwdPlan& pl, int chunk, int stages, cudaStream_t stream);
+int launch_bwd_pds(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream);
+int launch_bwd_grad(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream, int modes);
 size_t bwd_rowstat_elems(const splitd_params* p);
 size_t bwd_workspace_bytes(const splitd_params* p);
-int fill_bwd_params(const splitd_params* p, BwdParams& bp);
-int check_workspace(const splitd_params* p);
+size_t bwd_workspace_bytes_full(const splitd_params* p);
+size_t bwd_workspace_bytes_for(const splitd_params* p, size_t plane_limit);
+int plan_bwd(const splitd_params* p, BwdPlan& pl);
+void plan_chunk(const BwdPlan& pl, int i, const splitd_params* p, BwdParams& bp);
+int fill_bwd_params(const splitd_params* p, BwdParams& bp, const BwdPlan* pl);
+int check_common(const splitd_params* p, bool backward);
+int check_device();
+void clear_error();
 
 // Number of 2-CTA clusters of `kern` the current device keeps resident at once (the grid of a persistent
-// kernel). `cache` holds one entry per device index and is filled on first use.
+// kernel). `cache` holds one entry per device index and is filled on first use, which is also where the kernel's
+// dynamic shared memory limit is raised (once per device instead of once per launch). Concurrent first calls
+// compute the same value twice; the atomics only make that well defined. Returns <= 0 after a CUDA error.
 template <typename Kernel>
-inline int resident_cluster_pairs(Kernel kern, int threads, int smem_bytes, int (&cache)[64]) {
+inline int resident_cluster_pairs(Kernel kern, int threads, int smem_bytes, std::atomic<int> (&cache)[64]) {
   int dev = 0, resident = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_acquire);
+    if (c > 0) return c;
+  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2);
   cfg.blockDim = dim3(threads);
@@ -56,7 +92,7 @@ inline int resident_cluster_pairs(Kernel kern, int threads, int smem_bytes, int 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     resident = sms > 1 ? sms / 2 : 1;
   }
-  if (dev >= 0 && dev < 64) cache[dev] = resident;
+  if (dev >= 0 && dev < 64) cache[dev].store(resident, std::memory_order_release);
   return resident;
 }
 

@@ -48,9 +48,6 @@ static int scratch_base(unsigned char** out) {
   return 0;
 }
 
-int check_common(const splitd_params* p, bool backward);
-int check_device();
-
 }  // namespace sd
 
 using namespace sd;
@@ -61,6 +58,7 @@ size_t splitd_bwd_static_scratch_limit_workspace(void) { return kStaticWorkspace
 size_t splitd_bwd_static_scratch_limit_rowstat(void) { return kStaticStatElems; }
 
 int splitd_bwd_static_scratch(const splitd_params* p, void* stream) {
+  clear_error();
   if (!p) return fail(SPLITD_ERR_INVALID_ARGUMENT, "params is NULL");
   splitd_params q = *p;
   // placeholders so the shared argument checks see non-NULL scratch pointers
@@ -69,7 +67,7 @@ int splitd_bwd_static_scratch(const splitd_params* p, void* stream) {
   if (int e = check_common(&q, true)) return e;
   if (int e = check_device()) return e;
   const size_t need_stat = bwd_rowstat_elems(&q);
-  const size_t need_ws = bwd_workspace_bytes(&q);
+  const size_t need_ws = bwd_workspace_bytes_full(&q);  // everything in one piece: no chunking here
   if (need_stat > kStaticStatElems)
     return fail(SPLITD_ERR_WORKSPACE,
                 "problem too large for the static scratch: %zu row statistics needed, limit %zu "
@@ -86,12 +84,17 @@ int splitd_bwd_static_scratch(const splitd_params* p, void* stream) {
   q.lse_log2 = reinterpret_cast<float*>(base) + kStaticStatElems;
   q.workspace = base + 2 * kStaticStatElems * sizeof(float);
   q.workspace_bytes = kStaticWorkspaceBytes;
-  // Nothing in the scratch has to start at zero: every row statistic and every P / dS tile that a later
-  // kernel reads is written by an earlier kernel of the same call.
+  // The array keeps the previous call's contents. What must start at zero is the head of the workspace (the
+  // work counters of the persistent kernels and the running maxima the preprocess step collects); the
+  // preprocess launch clears it with a memset on `stream` first. Every row statistic and every P / dS tile
+  // that a later kernel reads is written by an earlier kernel of the same call.
+  BwdPlan pl;
+  if (int e = plan_bwd(&q, pl)) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int e = launch_bwd_preprocess(&q, s)) return e;
-  if (int e = launch_bwd_pds(&q, s)) return e;
-  return launch_bwd_grad(&q, s, 3);
+  for (int i = 0; i < pl.n_chunks; ++i)
+    if (int e = launch_bwd_chunk(&q, pl, i, 7, s)) return e;
+  return 0;
 }
 
 }  // extern "C"

@@ -20,6 +20,7 @@ enum : int {
   ST_TIMEOUT_SOFTMAX = 103,  // softmax / epilogue warps gave up waiting for an accumulator
   ST_TIMEOUT_PEER = 104,
   ST_BAD_SMEM_ALIGN = 105,   // dynamic shared memory not 1024-byte aligned
+  ST_BAD_SEQLEN = 106,       // packed layout: a sequence is longer than the max_seqlen_k the workspace was sized for
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -123,13 +124,16 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;  // 0.4 s per wait, then give up
+// A wait gives up after this long. It is far beyond anything a healthy kernel waits for (the longest legitimate
+// wait is one tile of another role, well under 10 ms) but leaves room for a context that is time-sliced or
+// preempted for a while; a kernel whose peer never arrives still ends instead of hanging the GPU.
+constexpr uint64_t kWaitLimitNs = 4000ull * 1000ull * 1000ull;
 
 // Bounded wait. `abort_flag` is a CTA-shared word: once any waiter in the CTA gave up, every later
 // wait returns false immediately so all roles unwind quickly.
 template <bool kClusterScope = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                int code, uint64_t limit_ns) {
   if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;  // fast path
   if (*abort_flag) return false;
   uint64_t t0 = 0;
@@ -140,13 +144,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
       }
     }
   }
+}
+template <bool kClusterScope = false>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  return mbar_wait_limit<kClusterScope>(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -266,9 +275,13 @@ __device__ __forceinline__ uint64_t desc_join(uint32_t lo) {
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major  [16] B major (0 = K-major, 1 = MN-major)  [17,23) N >> 3  [24,29) M >> 4
-__host__ __device__ constexpr uint32_t make_idesc(bool fp16, bool a_mn, bool b_mn, int M, int N) {
-  return (1u << 4) | ((fp16 ? 0u : 1u) << 7) | ((fp16 ? 0u : 1u) << 10) | ((a_mn ? 1u : 0u) << 15) |
+// A and B have format fields of their own: the two operands of one MMA may differ (fp16 x bf16).
+__host__ __device__ constexpr uint32_t make_idesc_ab(bool a_fp16, bool b_fp16, bool a_mn, bool b_mn, int M, int N) {
+  return (1u << 4) | ((a_fp16 ? 0u : 1u) << 7) | ((b_fp16 ? 0u : 1u) << 10) | ((a_mn ? 1u : 0u) << 15) |
          ((b_mn ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t make_idesc(bool fp16, bool a_mn, bool b_mn, int M, int N) {
+  return make_idesc_ab(fp16, fp16, a_mn, b_mn, M, N);
 }
 
 template <int kCtaGroup>
@@ -373,6 +386,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
   }
 }
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t mul_half2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// 2^e as a float for e in [-126, 127]
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }

@@ -5,7 +5,8 @@
 // warps) of both CTAs reads each entry once. The first tile of a pair is its own index, so no atomic sits
 // in front of the first load; later tiles come from `n_pairs + atomicAdd(counter, 1)`. A pair that ends
 // early simply draws more tiles, which is what balances tiles of unequal weight (causal masks, packed
-// sequences of different lengths). The counter must be zero when the kernel starts.
+// sequences of different lengths). The counter must be zero when the kernel starts; the last pair to draw from
+// it puts it back to zero (counted in a second word), so the next launch on the same workspace needs no memset.
 //
 // Every wait is bounded (mbar_wait): a role that gives up sets the CTA's abort flag and returns -1.
 #pragma once
@@ -36,8 +37,8 @@ __device__ __forceinline__ void tq_init(uint32_t base, int consumers_in_pair) {
 }
 
 // Scheduler loop, run by ONE thread of the leader CTA. Ends after publishing the first index >= total.
-__device__ __forceinline__ void tq_schedule(uint32_t base, int* counter, int pair_id, int n_pairs, int total,
-                                            volatile int* abort_flag, int* status) {
+__device__ __forceinline__ void tq_schedule(uint32_t base, int* counter, int* done, int pair_id, int n_pairs,
+                                            int total, volatile int* abort_flag, int* status) {
   const uint32_t peer_idx = mapa_u32(base, 1), peer_full = mapa_u32(base + 8, 1);
   for (int n = 0;; ++n) {
     const uint32_t slot = n & 1, ph = (n >> 1) & 1;
@@ -47,7 +48,16 @@ __device__ __forceinline__ void tq_schedule(uint32_t base, int* counter, int pai
     st_cluster_u32(peer_idx + 4 * slot, static_cast<uint32_t>(idx));
     mbar_arrive_cluster(mapa_u32(base + 8 + 8 * slot, 0));  // release at cluster scope orders the stores above
     mbar_arrive_cluster(peer_full + 8 * slot);
-    if (idx >= total) return;
+    if (idx >= total) {
+      // every pair ends with exactly one draw >= total; after the last of them nobody touches the counter again
+      __threadfence();
+      if (atomicAdd(done, 1) == n_pairs - 1) {
+        *counter = 0;
+        *done = 0;
+        __threadfence();
+      }
+      return;
+    }
   }
 }
 

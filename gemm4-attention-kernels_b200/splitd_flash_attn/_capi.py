@@ -21,6 +21,10 @@ EXPORTED_SYMBOLS = (
     "splitd_fwd",
     "splitd_bwd_rowstat_elems",
     "splitd_bwd_workspace_bytes",
+    "splitd_bwd_workspace_bytes_limit",
+    "splitd_bwd_num_chunks",
+    "splitd_bwd_chunk",
+    "splitd_wait_probe",
     "splitd_bwd_preprocess",
     "splitd_bwd_dq",
     "splitd_bwd_dkdv",
@@ -125,6 +129,14 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [pp]
         fn.restype = ctypes.c_size_t
+    lib.splitd_bwd_workspace_bytes_limit.argtypes = [pp, ctypes.c_size_t]
+    lib.splitd_bwd_workspace_bytes_limit.restype = ctypes.c_size_t
+    lib.splitd_bwd_num_chunks.argtypes = [pp]
+    lib.splitd_bwd_num_chunks.restype = ctypes.c_int
+    lib.splitd_bwd_chunk.argtypes = [pp, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    lib.splitd_bwd_chunk.restype = ctypes.c_int
+    lib.splitd_wait_probe.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p]
+    lib.splitd_wait_probe.restype = ctypes.c_int
     for name in ("splitd_bwd_static_scratch_limit_rowstat", "splitd_bwd_static_scratch_limit_workspace"):
         fn = getattr(lib, name)
         fn.argtypes = []

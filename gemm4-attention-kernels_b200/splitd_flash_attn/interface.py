@@ -12,8 +12,10 @@ Forward accepts bf16 and fp16; training (any input requiring grad) is bf16 only.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -22,7 +24,50 @@ from . import _capi
 
 SUPPORTED_HEAD_DIM = 512
 
-__all__ = ["split_flash_attn_func", "split_flash_attn_varlen_func"]
+__all__ = [
+    "split_flash_attn_func",
+    "split_flash_attn_varlen_func",
+    "kernel_status",
+    "cu_seqlens_validation",
+    "set_backward_workspace_limit",
+]
+
+# Value checks of cu_seqlens (first entry 0, last entry = token count, non-decreasing, max_seqlen large enough)
+# need the values on the host: one blocking device->host copy per tensor per call, in forward and again in
+# backward (the reference does the same with .item(), src/interface.py:164-172,187-188). A training loop that
+# builds its cu_seqlens correctly can switch them off; shape, dtype and device checks stay on.
+_VALIDATE_CU_SEQLENS = os.environ.get("SPLITD_VALIDATE_CU_SEQLENS", "1") != "0"
+
+
+@contextlib.contextmanager
+def cu_seqlens_validation(enabled: bool):
+    """``with cu_seqlens_validation(False): ...`` runs the packed API without any host synchronisation.
+
+    The caller then guarantees what the checks would have verified: cu_seqlens start at 0, end at the token
+    count, never decrease, and no sequence is longer than max_seqlen_q / max_seqlen_k. (A sequence with more
+    keys than max_seqlen_k is skipped by the backward kernels and reported through ``kernel_status()``.)
+    """
+    global _VALIDATE_CU_SEQLENS
+    old = _VALIDATE_CU_SEQLENS
+    _VALIDATE_CU_SEQLENS = bool(enabled)
+    try:
+        yield
+    finally:
+        _VALIDATE_CU_SEQLENS = old
+
+
+# Cap on the bytes of P / dS tiles the backward keeps in memory at once (None: the library's default, 6 GiB).
+# Larger problems are processed in chunks that reuse the same memory; results do not depend on it.
+_env_limit = os.environ.get("SPLITD_BWD_WORKSPACE_LIMIT_BYTES")
+_WORKSPACE_LIMIT: Optional[int] = int(_env_limit) if _env_limit else None
+
+
+def set_backward_workspace_limit(nbytes: Optional[int]) -> Optional[int]:
+    """Set the cap on the backward's tile memory (bytes; None = library default). Returns the old value."""
+    global _WORKSPACE_LIMIT
+    old = _WORKSPACE_LIMIT
+    _WORKSPACE_LIMIT = None if nbytes is None else int(nbytes)
+    return old
 
 
 # ---------------------------------------------------------------------------
@@ -85,8 +130,11 @@ def _validate_cu_seqlens(tensor, name, batch_size=None, total_tokens=None) -> No
         raise ValueError(f"{name} must be contiguous")
     if not tensor.is_cuda:
         raise RuntimeError(f"{name} must be on a CUDA device, got {tensor.device}")
+    if not _VALIDATE_CU_SEQLENS:
+        return None
     # one device->host copy for all value checks (the reference does three .item() syncs here)
     host = tensor.detach().cpu()
+    _raise_if_a_kernel_gave_up(tensor.device)  # the copy synchronised anyway: look at the status word too
     first = int(host[0])
     if first != 0:
         raise ValueError(f"{name}[0] must be 0, got {first}")
@@ -99,8 +147,9 @@ def _validate_cu_seqlens(tensor, name, batch_size=None, total_tokens=None) -> No
     return host
 
 
-def _validate_max_seqlen(host_cu, name, max_seqlen, max_name) -> None:
-    if host_cu is None:
+def _validate_max_seqlen(cu, host_cu, name, max_seqlen, max_name) -> None:
+    """`cu` is the device tensor (None = batched layout), `host_cu` its host copy (None = value checks are off)."""
+    if cu is None:
         return
     if max_seqlen is None:
         raise ValueError(f"{max_name} must be provided when {name} is provided")
@@ -108,6 +157,8 @@ def _validate_max_seqlen(host_cu, name, max_seqlen, max_name) -> None:
         raise TypeError(f"{max_name} must be an int, got {type(max_seqlen).__name__}")
     if max_seqlen < 0:
         raise ValueError(f"{max_name} must be non-negative, got {max_seqlen}")
+    if host_cu is None:
+        return
     lengths = host_cu[1:] - host_cu[:-1]
     actual_max = int(lengths.max()) if lengths.numel() > 0 else 0
     if max_seqlen < actual_max:
@@ -222,9 +273,34 @@ def _status_flag(device: torch.device) -> torch.Tensor:
 
 
 def kernel_status(device: Optional[torch.device] = None) -> int:
-    """Synchronise and return the device status word (0 = no kernel gave up a bounded wait)."""
+    """Synchronise and return the device's status word: 0 = every kernel of this library ran to its end.
+
+    The kernels never spin forever: a wait that exceeds 4 s is given up, the kernel ends early and stores a
+    code here (101 loads, 102 tensor-core issue, 103 softmax/epilogue, 104 peer CTA, 105 shared-memory
+    alignment, 106 a packed sequence longer than max_seqlen_k). Outputs of such a call are incomplete. The calls
+    of this module are asynchronous, so nothing can raise at the call itself: check this after a step (it costs
+    one 4-byte copy), e.g. where the loss is read. The packed API looks at it whenever it validates cu_seqlens.
+    ``reset_kernel_status()`` re-arms it.
+    """
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     return int(_status_flag(device).item())
+
+
+def reset_kernel_status(device: Optional[torch.device] = None) -> None:
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    _status_flag(device).zero_()
+
+
+def _raise_if_a_kernel_gave_up(device: torch.device) -> None:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    flag = _status_flags.get(key)
+    if flag is not None:
+        code = int(flag.item())
+        if code != 0:
+            raise RuntimeError(
+                f"an earlier SplitD attention kernel on {device} ended early with status {code} "
+                "(see kernel_status); its outputs are incomplete"
+            )
 
 
 def _strides3(t: torch.Tensor, packed: bool):
@@ -316,8 +392,8 @@ def _flash_attn_fwd(
     )
     requires_grad = q.requires_grad or k.requires_grad or v.requires_grad
     _validate_training_dtype(q, requires_grad)
-    _validate_max_seqlen(host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
-    _validate_max_seqlen(host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
+    _validate_max_seqlen(cu_seqlens_q, host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
+    _validate_max_seqlen(cu_seqlens_k, host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
     if (cu_seqlens_q is None) != (cu_seqlens_k is None):
         raise ValueError("cu_seqlens_q and cu_seqlens_k must be given together")
     _validate_device_arch(q.device)
@@ -394,8 +470,8 @@ def _flash_attn_bwd(
     (batch_size, seqlen_q, total_q, seqlen_k, num_head, num_head_kv, host_cu_q, host_cu_k) = _validate_qkv_common(
         q, k, v, cu_seqlens_q, cu_seqlens_k
     )
-    _validate_max_seqlen(host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
-    _validate_max_seqlen(host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
+    _validate_max_seqlen(cu_seqlens_q, host_cu_q, "cu_seqlens_q", max_seqlen_q, "max_seqlen_q")
+    _validate_max_seqlen(cu_seqlens_k, host_cu_k, "cu_seqlens_k", max_seqlen_k, "max_seqlen_k")
     if q.dtype == torch.float16:
         raise NotImplementedError("SplitD backward currently supports bfloat16 only.")
     device = q.device
@@ -432,7 +508,10 @@ def _flash_attn_bwd(
     params.dv_strides[:] = _strides3(dv, packed)
     lib = _capi.load_library()
     n_stat = lib.splitd_bwd_rowstat_elems(ctypes.byref(params))
-    n_ws = lib.splitd_bwd_workspace_bytes(ctypes.byref(params))
+    if _WORKSPACE_LIMIT is None:
+        n_ws = lib.splitd_bwd_workspace_bytes(ctypes.byref(params))
+    else:
+        n_ws = lib.splitd_bwd_workspace_bytes_limit(ctypes.byref(params), _WORKSPACE_LIMIT)
     dpsum = torch.empty(n_stat, dtype=torch.float32, device=device)
     lse_log2 = torch.empty(n_stat, dtype=torch.float32, device=device)
     workspace = torch.empty(n_ws, dtype=torch.uint8, device=device)
@@ -442,16 +521,24 @@ def _flash_attn_bwd(
         if stage_events is None:
             _capi.check(lib.splitd_bwd(ctypes.byref(params), _stream_ptr(device)))
         else:
-            # same three launches, with a CUDA event before each and one after the last (profiling)
-            # (preprocess, P/dS tiles, gradient GEMMs: exactly the launches splitd_bwd makes)
-            for fn in (lib.splitd_bwd_preprocess, lib.splitd_bwd_tiles, lib.splitd_bwd_grads):
+            # the launches splitd_bwd makes (preprocess; per chunk: P/dS tiles, gradient GEMMs), with a CUDA event
+            # in front of each and one after the last: (label, event) pairs for per-kernel timing
+            def mark(label):
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record()
-                stage_events.append(ev)
-                _capi.check(fn(ctypes.byref(params), _stream_ptr(device)))
-            ev = torch.cuda.Event(enable_timing=True)
-            ev.record()
-            stage_events.append(ev)
+                stage_events.append((label, ev))
+
+            mark("bwd_preprocess")
+            _capi.check(lib.splitd_bwd_preprocess(ctypes.byref(params), _stream_ptr(device)))
+            n_chunks = lib.splitd_bwd_num_chunks(ctypes.byref(params))
+            if n_chunks < 0:
+                _capi.check(n_chunks)
+            for c in range(n_chunks):
+                mark("bwd_tiles")
+                _capi.check(lib.splitd_bwd_chunk(ctypes.byref(params), c, 1, _stream_ptr(device)))
+                mark("bwd_grads")
+                _capi.check(lib.splitd_bwd_chunk(ctypes.byref(params), c, 2, _stream_ptr(device)))
+            mark("end")
     return dq, dk, dv
 
 
@@ -657,8 +744,137 @@ torch.library.register_autograd("splitd_flash_attn::varlen_fwd", _varlen_backwar
 
 
 # ---------------------------------------------------------------------------
+# PyTorch custom ops for the batched layout: ``splitd_flash_attn::fwd`` / ``::bwd``. The reference registers
+# ops for the packed layout only and runs the batched one through ``FlashAttnFunc`` (interface.py:1117-1173);
+# with an op pair of its own the batched call is traceable by FakeTensor / torch.compile too. Same encoding of
+# the optional window ints as above.
+# ---------------------------------------------------------------------------
+
+
+@torch.library.custom_op("splitd_flash_attn::fwd", mutates_args=())
+def _fwd_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    pack_gqa: bool,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    return _flash_attn_fwd(
+        q,
+        k,
+        v,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        softcap=softcap,
+        pack_gqa=pack_gqa,
+        return_lse=True,
+    )
+
+
+def _fake_shapes_batched(q, k, v):
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k and v must be rank-4 (batch, seqlen, heads, head_dim) tensors")
+    _validate_head_dims(q.shape[-1], v.shape[-1])
+    if q.shape[-2] % k.shape[-2] != 0:
+        raise ValueError(f"num_head ({q.shape[-2]}) must be divisible by num_head_kv ({k.shape[-2]})")
+
+
+@torch.library.register_fake("splitd_flash_attn::fwd")
+def _fwd_fake(q, k, v, softmax_scale, causal, window_size_left, window_size_right, softcap, pack_gqa):
+    _fake_shapes_batched(q, k, v)
+    _validate_training_dtype(q, q.requires_grad or k.requires_grad or v.requires_grad)
+    out = q.new_empty((q.shape[0], q.shape[1], q.shape[2], v.shape[-1]))
+    lse = q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
+    return out, lse
+
+
+@torch.library.custom_op("splitd_flash_attn::bwd", mutates_args=())
+def _bwd_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    dout: torch.Tensor,
+    lse: torch.Tensor,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    dlse: Optional[torch.Tensor],
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _flash_attn_bwd(
+        q,
+        k,
+        v,
+        out,
+        dout,
+        lse,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        softcap=softcap,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        dlse=dlse,
+    )
+
+
+@torch.library.register_fake("splitd_flash_attn::bwd")
+def _bwd_fake(q, k, v, out, dout, lse, softmax_scale, causal, window_size_left, window_size_right, softcap, dlse):
+    _fake_shapes_batched(q, k, v)
+    if q.dtype == torch.float16:
+        raise NotImplementedError("SplitD backward currently supports bfloat16 only.")
+    if softcap != 0.0:
+        raise NotImplementedError("SplitD backward does not support softcap yet")
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _batched_setup_context(ctx, inputs, output) -> None:
+    q, k, v = inputs[:3]
+    ctx.softmax_scale, ctx.causal, ctx.window_size_left, ctx.window_size_right, ctx.softcap = inputs[3:8]
+    out, lse = output
+    ctx.save_for_backward(q, k, v, out, lse)
+    ctx.set_materialize_grads(False)
+
+
+def _batched_backward(ctx, dout, dlse):
+    q, k, v, out, lse = ctx.saved_tensors
+    if dout is None:
+        dout = torch.zeros_like(out)
+    dq, dk, dv = torch.ops.splitd_flash_attn.bwd(
+        q, k, v, out, dout, lse, ctx.softmax_scale, ctx.causal, ctx.window_size_left, ctx.window_size_right,
+        ctx.softcap, dlse,
+    )
+    return dq, dk, dv, *((None,) * 6)
+
+
+torch.library.register_autograd("splitd_flash_attn::fwd", _batched_backward, setup_context=_batched_setup_context)
+
+
+# ---------------------------------------------------------------------------
 # public API
 # ---------------------------------------------------------------------------
+
+
+def _reject_unsupported_training(q, k, v, softcap, window_size) -> None:
+    """Inside a custom op the tensors no longer say whether they require grad, so what training does not
+    support (fp16, softcap, sliding windows; interface.py:133-138,264-286 of the reference) is refused here."""
+    tensors = [t for t in (q, k, v) if isinstance(t, torch.Tensor)]
+    if not (torch.is_grad_enabled() and any(t.requires_grad for t in tensors)):
+        return
+    _validate_training_dtype(q, True)
+    if isinstance(window_size, tuple) and len(window_size) == 2:
+        try:
+            _, local = _resolve_causal_local_window(False, window_size[0], window_size[1])
+        except ValueError:
+            local = False
+        _unsupported_features(True, softcap, local)
 
 
 def split_flash_attn_func(
@@ -675,9 +891,28 @@ def split_flash_attn_func(
     """Batched SplitD FlashAttention for D=512 (interface.py:1226-1252 of the reference).
 
     q (B, Sq, Hq, 512), k/v (B, Sk, Hkv, 512) with Hq % Hkv == 0. Returns ``out`` or ``(out, lse)``.
-    Training requires bf16 q/k/v; fp16 is accepted only for no-grad forward.
+    Training requires bf16 q/k/v; fp16 is accepted only for no-grad forward. Runs through the
+    ``splitd_flash_attn::fwd`` / ``::bwd`` custom ops (``FlashAttnFunc`` is the same thing as a plain
+    autograd.Function, as in the reference).
     """
-    out, lse = FlashAttnFunc.apply(q, k, v, softmax_scale, causal, window_size, softcap, pack_gqa, return_lse)
+    if not isinstance(window_size, tuple) or len(window_size) != 2:
+        raise TypeError("window_size must be a tuple of (left, right)")
+    _reject_unsupported_training(q, k, v, softcap, window_size)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    if pack_gqa is None:
+        pack_gqa = q.ndim == 4 and k.ndim == 4 and q.shape[-2] > k.shape[-2]
+    out, lse = torch.ops.splitd_flash_attn.fwd(
+        q,
+        k,
+        v,
+        float(softmax_scale),
+        bool(causal),
+        _enc(window_size[0]),
+        _enc(window_size[1]),
+        float(softcap),
+        bool(pack_gqa),
+    )
     return (out, lse) if return_lse else out
 
 
@@ -715,6 +950,7 @@ def split_flash_attn_varlen_func(
         raise NotImplementedError("aux_tensors is not supported by the SplitD varlen path")
     if not isinstance(window_size, tuple) or len(window_size) != 2:
         raise TypeError("window_size must be a tuple of (left, right)")
+    _reject_unsupported_training(q, k, v, softcap, window_size)
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
     if pack_gqa is None:

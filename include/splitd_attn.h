@@ -57,8 +57,8 @@ typedef struct {
   void* dv;          /* like v                                                    */
   float* dpsum;      /* fp32 scratch, splitd_bwd_rowstat_elems() elements          */
   float* lse_log2;   /* fp32 scratch, same size                                   */
-  void* workspace;   /* bf16 P / dS tile scratch, splitd_bwd_workspace_bytes()     */
-  size_t workspace_bytes;
+  void* workspace;   /* scratch for the P / dS tiles (fp16), 256-byte aligned; see splitd_bwd_workspace_bytes() */
+  size_t workspace_bytes; /* how much of it the library may use                    */
 
   /* ---- packed (varlen) layout; both NULL selects the batched layout ---- */
   const int32_t* cu_seqlens_q; /* device, B+1 entries */
@@ -68,7 +68,9 @@ typedef struct {
   int32_t batch;
   int32_t seqlen_q, seqlen_k; /* batched: S; packed: ignored                              */
   int32_t total_q, total_k;   /* packed: T; batched: ignored                              */
-  int32_t max_seqlen_q, max_seqlen_k; /* packed: upper bounds on the sequence lengths     */
+  int32_t max_seqlen_q, max_seqlen_k; /* packed: upper bounds on the sequence lengths. The backward sizes its
+                                         tile rows by max_seqlen_k; a sequence with more keys than that is
+                                         skipped and reported through status_flag (code 106)               */
   int32_t heads_q, heads_kv, head_dim;
 
   /* ---- strides in elements: {batch, sequence (token), head}; packed layout ignores [0] ---- */
@@ -79,12 +81,14 @@ typedef struct {
   int32_t causal;      /* 0 / 1 */
   int32_t dtype;       /* SPLITD_DTYPE_* of q, k, v, o, dout, dq, dk, dv */
 
-  /* device word; a kernel that gives up a bounded wait stores a positive code here (0 = fine). */
-  int32_t* status_flag; /* may be NULL */
+  /* device word, may be NULL. Every wait inside the kernels is bounded (4 s); a kernel that gives one up stores a
+     positive code here with compare-and-swap against 0 and ends early, leaving its outputs incomplete:
+     101 loads, 102 tensor-core issue, 103 softmax / epilogue, 104 peer CTA, 105 misaligned shared memory,
+     106 a packed sequence longer than max_seqlen_k. 0 = fine. Read it after synchronising; zero it to re-arm. */
+  int32_t* status_flag;
 
-  /* optional fp32 device buffer of at least 64 elements receiving per-role cycle counters of one CTA pair
-     (tests / tuning only): [0,8) P/dS kernel, [8,16) gradient kernel, [32,52) forward kernel; element 35
-     holds, as an int32, the cycle count / 1024 of the forward's longest-running CTA pair (zero it first) */
+  /* reserved, must be NULL. (Builds made with -DSPLITD_PROFILE write per-role cycle counters of one CTA pair
+     to the 64 floats it then points to.) */
   float* debug;
 
   /* ---- forward-only score modifiers (the backward rejects them, like src/interface.py:676-683) ---- */
@@ -105,21 +109,37 @@ int splitd_device_supported(int device);
  * (src/interface.py:538-553, kernel src/flash_fwd_sm90_d512.py). bf16 or fp16. */
 int splitd_fwd(const splitd_params* p, void* stream);
 
-/* Number of fp32 elements the caller must provide in each of `dpsum` and `lse_log2`
- * (row statistics, padded per sequence; src/interface.py:747-753). */
+/* Number of fp32 elements the caller must provide in each of `dpsum` and `lse_log2`: one per (query row,
+ * query head), batch * heads_q * seqlen_q or heads_q * total_q, no padding (src/interface.py:747-753 pads the
+ * reference's to multiples of 64 per sequence; here tail rows are masked in the kernels instead). */
 size_t splitd_bwd_rowstat_elems(const splitd_params* p);
 
-/* Bytes of `workspace` the backward needs for the given problem. */
+/* The backward's scratch. The reference's kernels recompute S and dP in every head_dim pass and need no more
+ * than the two row vectors above (src/interface.py:747-753); this library computes them once and hands the
+ * P and dS tiles to the gradient GEMMs through `workspace` in fp16, 4 bytes per (query, key) pair and query head.
+ * The workspace does NOT have to hold all of them: splitd_bwd cuts the problem into chunks of (KV heads, batches)
+ * or, when one KV head of one batch is still too large, of row ranges whose dK/dV partial sums travel from chunk to chunk
+ * in fp32, and reuses the same tile memory for every chunk. Results do not depend on the chunking, bit for bit.
+ *   splitd_bwd_workspace_bytes(p)            what to allocate by default: everything at once if the tiles take at
+ *                                            most 6 GiB, else 6 GiB of tiles plus the fixed parts;
+ *   splitd_bwd_workspace_bytes_limit(p, n)   the same with your own cap n on the tile bytes; n = 0 gives the
+ *                                            smallest workspace splitd_bwd accepts, n = SIZE_MAX the size that
+ *                                            holds the whole problem in one chunk.
+ * Any workspace_bytes between those two extremes is accepted; more memory means fewer, larger launches. */
 size_t splitd_bwd_workspace_bytes(const splitd_params* p);
+size_t splitd_bwd_workspace_bytes_limit(const splitd_params* p, size_t tile_bytes_limit);
 
 /* Backward step 1: dpsum = rowsum(o * dout) - dlse, lse_log2 = lse * log2(e).
  * Replaces `_bwd_preprocess.compile_cache[key](out,dout,dpsum,lse,lse_log2,None,cu_q,None,dlse)`
- * (src/interface.py:615-641, kernel src/flash_bwd_preprocess.py). */
+ * (src/interface.py:615-641, kernel src/flash_bwd_preprocess.py). Also clears the head of `workspace` (work
+ * counters) and collects there the per-(batch, KV head) maxima that scale dS for fp16; every other backward
+ * step relies on it having run first on the same workspace. */
 int splitd_bwd_preprocess(const splitd_params* p, void* stream);
 
 /* Backward step 2: dq. Replaces the dQ call `(q,k,v,dout,lse_log2,dpsum,dq,scale,cu_q,cu_k)`
- * (src/interface.py:875-886, kernel src/fmha_dq_sm90_d512.py). Also leaves the bf16 P and dS
- * tiles of every (query tile, key tile) pair in `workspace` for step 3. */
+ * (src/interface.py:875-886, kernel src/fmha_dq_sm90_d512.py). Also leaves the P and dS tiles of every
+ * (query tile, key tile) pair in `workspace` for step 3, which is why this two-call form needs the workspace
+ * of splitd_bwd_workspace_bytes_limit(p, SIZE_MAX) (SPLITD_ERR_WORKSPACE otherwise). */
 int splitd_bwd_dq(const splitd_params* p, void* stream);
 
 /* Backward step 3: dk, dv, reduced over the Hq/Hkv query heads of each KV head.
@@ -128,17 +148,22 @@ int splitd_bwd_dq(const splitd_params* p, void* stream);
  * the same stream with the same params. */
 int splitd_bwd_dkdv(const splitd_params* p, void* stream);
 
-/* The two steps splitd_bwd is made of after the preprocess step, for callers that want to time or schedule
- * them separately (no counterpart in the reference, whose kernels recompute instead):
- * splitd_bwd_tiles writes the bf16 P and dS tiles to `workspace` (S = QK^T and dP = dO V^T on the tensor
- * cores, as two alternating GEMM passes; SPLITD_PDS_ONE_PASS=1 in the environment selects a kernel that does
- * both GEMMs per key block instead and is a little slower); splitd_bwd_grads computes dq, dk and dv from them
- * in one launch. */
+/* The two launches behind steps 2 and 3, for callers that want to time or schedule them separately (no
+ * counterpart in the reference, whose kernels recompute instead): splitd_bwd_tiles writes the P and dS tiles
+ * (S = QK^T and dP = dO V^T on the tensor cores, as two alternating GEMM passes); splitd_bwd_grads computes dq,
+ * dk and dv from them in one launch. Whole problem in one chunk, like splitd_bwd_dq. */
 int splitd_bwd_tiles(const splitd_params* p, void* stream);
 int splitd_bwd_grads(const splitd_params* p, void* stream);
 
-/* All three backward steps in order on `stream` (what _flash_attn_bwd_sm90 does,
- * src/interface.py:652-888). */
+/* The same two launches chunk by chunk, for any workspace splitd_bwd accepts: splitd_bwd_num_chunks returns how
+ * many chunks the given workspace_bytes lead to (or a negative status); splitd_bwd_chunk runs `stages` (1 = tiles,
+ * 2 = gradients, 3 = both) of chunk `chunk`. Chunks must run in order 0, 1, ... on one stream, tiles before
+ * gradients, after splitd_bwd_preprocess: dk/dv of a KV head whose rows are spread over chunks accumulate. */
+int splitd_bwd_num_chunks(const splitd_params* p);
+int splitd_bwd_chunk(const splitd_params* p, int chunk, int stages, void* stream);
+
+/* All backward steps in order on `stream` (what _flash_attn_bwd_sm90 does, src/interface.py:652-888):
+ * preprocess, then tiles + gradients for every chunk. */
 int splitd_bwd(const splitd_params* p, void* stream);
 
 /* Backward (all three steps, like splitd_bwd) that allocates NOTHING and needs no scratch from the caller.
@@ -147,8 +172,8 @@ int splitd_bwd(const splitd_params* p, void* stream);
  * all device memory and hands out only the tensors of the op, a process that was given a fixed memory budget. The scratch (dpsum, lse_log2 and
  * the P/dS workspace; those three fields of `p` are ignored) is a 17 MiB array compiled into the library
  * and resident on every GPU that loads it until the process exits.
- *  - Limits: splitd_bwd_rowstat_elems(p) <= 65536 and splitd_bwd_workspace_bytes(p) <= 16 MiB
- *    (e.g. B=1, S=512, Hq=8, Hkv=1). Larger problems return SPLITD_ERR_WORKSPACE with a message that says
+ *  - Limits: splitd_bwd_rowstat_elems(p) <= 65536 and splitd_bwd_workspace_bytes_limit(p, SIZE_MAX) <= 16 MiB
+ *    (e.g. B=1, S=512, Hq=8, Hkv=1): the problem is run in one chunk. Larger problems return SPLITD_ERR_WORKSPACE with a message that says
  *    which limit was hit; use splitd_bwd with your own buffers for those.
  *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
  *    device current). Make that first call outside any stream capture.
@@ -157,6 +182,12 @@ int splitd_bwd(const splitd_params* p, void* stream);
 int splitd_bwd_static_scratch(const splitd_params* p, void* stream);
 size_t splitd_bwd_static_scratch_limit_rowstat(void);   /* 65536 floats   */
 size_t splitd_bwd_static_scratch_limit_workspace(void); /* 16 MiB         */
+
+/* Test aid, on no product path: one small CTA waits with the kernels' bounded wait on a barrier that nobody
+ * arrives on, for limit_us microseconds (1 .. 100000), then stores code 104 in *status_flag (device memory)
+ * and the time it waited in *waited_ns (device memory, may be NULL) and ends normally. It shows that a wait
+ * that runs out leaves the kernel, the context and the GPU in working order. No counterpart in the reference. */
+int splitd_wait_probe(int32_t* status_flag, unsigned int limit_us, unsigned long long* waited_ns, void* stream);
 
 /* Message of the last failure on this thread ("" if none). */
 const char* splitd_last_error(void);
