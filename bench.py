@@ -2,6 +2,8 @@
 """Benchmark of the D=512 SplitD attention path (forward + backward) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case B,S[,causal] [--iters N] [--no-backward] [--heads HQ,HKV]   # one shape, per-kernel times
+    python bench.py --case packed:32768,causal                                        # packed layout, random lengths
 
 One STEP is one pass of the reference's benchmark sweep (scripts/bench_splitd_512_gqa_bs16k.py:51-60):
 bf16, Hq=32, Hkv=4, D=512, fixed B*S=16384 with (B,S) in {(16,1024),(8,2048),(4,4096),(2,8192),(1,16384)},
@@ -13,7 +15,10 @@ FLOPs: 4*B*Hq*Sq*Sk*D (x0.5 causal) forward, 2.5x that backward (src/bench_utils
 same metric through the public API (split_flash_attn_func + autograd) with pinned HOST buffers, host->device
 copies of q,k,v,dO and device->host copies of out,dq,dk,dv inside the timed region.
 With N>1 (torchrun) every rank runs the same sweep on its own seed (weak scaling; no collective on the
-data path; NCCL only for the barrier and the max-over-ranks time).
+data path; NCCL only for the barrier and the max-over-ranks time). Besides the sweep, every run times the
+Gemma-4-31B-shaped layer (B=2, S=32768, Hq=32, Hkv=4, causal) as 8 (batch, kv-head group) shards dealt round-robin
+to the N ranks (`config5`: strong scaling, identical data at every N), and the forward sweep's fp16 repeat.
+--case times a single shape per kernel and prints text: the small, self-terminating command to put under ncu.
 
 --impl reference times the reference's CPU path (its pure-PyTorch fp32 attention, restated in
 oracle/attention_oracle.py) on the host cores for the same metric on a bounded sample.
@@ -170,7 +175,7 @@ def run_ours(args):
     if world > 1:
         # stdout carries the one JSON line only: NCCL's own output (its version banner is printed from level
         # WARN up) goes to stderr
-        os.environ["NCCL_DEBUG"] = os.environ.get("SPLITD_NCCL_DEBUG", "WARN")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
@@ -191,7 +196,7 @@ def run_ours(args):
     total_flops = 3.5 * total_fwd
 
     # per-kernel event times, accumulated over the timed steps
-    kt = {"fwd": 0.0, "bwd_preprocess": 0.0, "bwd_tiles": 0.0, "bwd_grads": 0.0}
+    kt = {"fwd": 0.0, "bwd_preprocess": 0.0, "bwd_tiles": 0.0, "bwd_grads": 0.0}  # bwd_preprocess = row maxima + preprocess
     per_case = {}
 
     def one_step(record):
@@ -203,9 +208,10 @@ def run_ours(args):
             out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True)
             evs = []
             I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs)
-            launches += 4  # forward, preprocess, P/dS tiles, gradient GEMMs
+            # forward; row maxima + preprocess; per chunk of the backward: P/dS tiles, gradient GEMMs
+            launches += 1 + 2 + (len(evs) - 2)
             if record is not None:
-                record.append(((B, S, causal), [e0] + evs))
+                record.append(((B, S, causal), [("fwd", e0)] + evs))
         return launches
 
     for _ in range(args.warmup):
@@ -227,41 +233,53 @@ def run_ours(args):
         raise RuntimeError("a kernel gave up a bounded wait during the benchmark")
 
     for key, evs in records:
-        names = ["fwd", "bwd_preprocess", "bwd_tiles", "bwd_grads"]
-        ts = [evs[i].elapsed_time(evs[i + 1]) for i in range(4)]
-        for n, t in zip(names, ts):
-            kt[n] += t
-        c = per_case.setdefault(key, [0.0, 0.0, 0])
-        c[0] += ts[0]
-        c[1] += ts[1] + ts[2] + ts[3]
+        c = per_case.setdefault(key, [0.0, 0.0, 0, 0])
+        for (label, ev), (_, nxt) in zip(evs[:-1], evs[1:]):
+            t = ev.elapsed_time(nxt)
+            kt[label] += t
+            c[0 if label == "fwd" else 1] += t
         c[2] += 1
+        c[3] = sum(1 for label, _ in evs if label == "bwd_tiles")
     sweep = []
-    for (B, S, causal), (tf, tb, n) in per_case.items():
+    for (B, S, causal), (tf, tb, n, n_chunks) in per_case.items():
         f = flops_fwd(B, S, causal)
-        sweep.append({"B": B, "S": S, "causal": causal, "fwd_ms": tf / n, "bwd_ms": tb / n,
-                      "fwd_tflops": f / (tf / n) / 1e9, "bwd_tflops": 2.5 * f / (tb / n) / 1e9})
+        sweep.append({"B": B, "S": S, "causal": causal, "dtype": "bf16", "fwd_ms": tf / n, "bwd_ms": tb / n,
+                      "fwd_tflops": f / (tf / n) / 1e9, "bwd_tflops": 2.5 * f / (tb / n) / 1e9,
+                      "fwd_frac_of_peak": f / (tf / n) / 1e9 / load_peaks()[0],
+                      "bwd_frac_of_peak": 2.5 * f / (tb / n) / 1e9 / load_peaks()[0], "bwd_chunks": n_chunks})
     n_steps = args.steps
     fwd_tflops = total_fwd * n_steps / kt["fwd"] / 1e9
     bwd_tflops = 2.5 * total_fwd * n_steps / (kt["bwd_preprocess"] + kt["bwd_tiles"] + kt["bwd_grads"]) / 1e9
 
     # ---- roofline of the dominant kernel (tensor bound). Algorithmic FLOPs per launch, with F = forward FLOPs:
     #      forward kernel F; P/dS tile kernel F (S and dP GEMMs); gradient GEMM kernel 1.5 F (dQ, dK, dV).
-    #      DRAM traffic per launch: ncu capture at B=1,S=4096 non-causal (profiles/), scaled by FLOPs -- the
-    #      workspace traffic of both backward kernels grows with rows*keys, i.e. in proportion to the FLOPs.
     peak, peak_sus, peak_kind = load_peaks()
     algo = {"fwd": total_fwd, "bwd_tiles": total_fwd, "bwd_grads": 1.5 * total_fwd}
-    #      The forward's traffic is its operands and output once (0.274 GB at B*S = 4096), so it scales with
-    #      B*S (x4 for every shape of the sweep), not with the FLOPs.
-    dram_bytes_per_flop = {"fwd": None, "bwd_tiles": 3.126e9 / 1.0995e12, "bwd_grads": 3.83e9 / (1.5 * 1.0995e12)}
-    fwd_dram_bytes_per_launch = 0.266e9 * (16384 / 4096)
     dom = max(algo, key=lambda n: kt[n])
     achieved = algo[dom] * n_steps / kt[dom] / 1e9
     n_launch = len(cases)
-    traffic = fwd_dram_bytes_per_launch if dom == "fwd" else dram_bytes_per_flop[dom] * algo[dom] / n_launch
+    # DRAM bytes per launch of the dominant kernel, averaged over the sweep's shapes: a MODEL, not a counter (ncu
+    # cannot run inside the timed region). Per shape, with T = 16384 tokens and PS = 2 B x (query heads x rows x
+    # causally visible keys) for one of the P / dS planes:
+    #   forward         q, k, v read + o written once;
+    #   P/dS tiles      q, dout, k, v read + P written, P read back (L2 hits are not subtracted), dS written;
+    #   gradient GEMMs  P read once (dV), dS read twice (dK, dQ) + fp16 dO, Q, K read + dq, dk, dv written.
+    # profiles/ holds the ncu captures of the same kernels at B=1, S=4096 as the cross-check of this model.
+    tok = 16384
+    q_bytes, kv_bytes = tok * HQ * D * 2, tok * HKV * D * 2
+
+    def plane(B, S, causal):
+        return 2.0 * B * HQ * S * S * (0.5 if causal else 1.0)
+
+    model = {"fwd": sum(2 * q_bytes + 2 * kv_bytes for _ in cases) / n_launch,
+             "bwd_tiles": sum(2 * q_bytes + 2 * kv_bytes + 3 * plane(*c) for c in cases) / n_launch,
+             "bwd_grads": sum(3 * q_bytes + 3 * kv_bytes + 3 * plane(*c) for c in cases) / n_launch}
+    traffic = model[dom]
     # The kernels are timed back to back inside a step of ~0.2 s that runs under the power cap, so the
     # denominator is the sustained cuBLAS figure; the burst figure (a kernel timed alone) is given beside it.
     roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak_sus, "unit": "TFLOP/s",
-                "frac": achieved / peak_sus, "traffic": traffic, "traffic_note": "avg DRAM bytes per launch, scaled from an ncu capture",
+                "frac": achieved / peak_sus, "traffic": traffic,
+                "traffic_note": "model estimate of the DRAM bytes per launch (operands + P/dS planes, see bench.py); ncu captures of the same kernels at B=1,S=4096 are in profiles/",
                 "peak_source": f"{peak_kind} bf16 sustained (kernel timed inside a long step under sw_power_cap)",
                 "peak_burst": peak, "frac_of_burst": achieved / peak,
                 "per_kernel_tflops": {n: algo[n] * n_steps / kt[n] / 1e9 for n in algo},
@@ -325,47 +343,177 @@ def run_ours(args):
     e2e_ms = sharding.max_over_ranks(s0.elapsed_time(s1), dev)
     e2e_val = world * total_flops * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_steps else None
 
-    # ---- the two other GPU configurations of the reference's plan, timed once outside the step (N=1 only):
-    #      the packed causal training step (sequence lengths uniform in [128, 8192], 32768 tokens, seed 0) and
-    #      one (batch, kv-head group) shard of the B=2, S=32768, Hq=32, Hkv=4 causal layer (B=1, Hq=8, Hkv=1).
+    del q, k, v, do
+    torch.cuda.empty_cache()
+
+    def timed(fn, iters=3):
+        """fn() -> list of (label, event) ending with ("end", event). Per-label times of the fastest of the
+        iterations after the first (warm-up) one."""
+        runs = []
+        for _ in range(iters):
+            evs = fn()
+            torch.cuda.synchronize(dev)
+            ts = {}
+            for (label, ev), (_, nxt) in zip(evs[:-1], evs[1:]):
+                ts[label] = ts.get(label, 0.0) + ev.elapsed_time(nxt)
+            runs.append(ts)
+        return min(runs[1:], key=lambda ts: sum(ts.values()))
+
+    def fwd_bwd_events(qq, kk, vv, dd, causal, backward=True, **kw):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True, **kw)
+        evs = [("fwd", e0)]
+        if backward:
+            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs, **kw)
+        else:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            evs.append(("end", e1))
+        return evs
+
+    # ---- the fp16 repeat of the forward sweep at S = 4096 (forward only: training is bf16), rank 0
+    fp16_rows = []
+    if rank == 0 and not args.skip_e2e:
+        mk16 = lambda h: torch.randn(4, 4096, h, D, device=dev).to(torch.float16)
+        q16, k16, v16 = mk16(HQ), mk16(HKV), mk16(HKV)
+        for causal in (False, True):
+            t = timed(lambda: fwd_bwd_events(q16, k16, v16, None, causal, backward=False))["fwd"]
+            f = flops_fwd(4, 4096, causal)
+            fp16_rows.append({"B": 4, "S": 4096, "causal": causal, "dtype": "fp16", "fwd_ms": t,
+                              "fwd_tflops": f / t / 1e9, "fwd_frac_of_peak": f / t / 1e9 / peak})
+        del q16, k16, v16
+
+    # ---- the Gemma-4-31B-shaped layer: B=2, S=32768, Hq=32, Hkv=4, causal, as 8 (batch, kv-head group) shards on
+    #      strided views of one tensor set, dealt round-robin to the ranks (strong scaling; every shard's data is
+    #      seeded by the shard id, so every N sees the same numbers). No collective on the data path; NCCL carries
+    #      the barrier, the max-over-ranks time and the per-shard check results.
+    config5 = None
+    if not args.skip_e2e:
+        LB, LS, G = 2, 32768, HQ // HKV
+        shards = sharding.layer_shards(LB, HKV)
+        mine = sharding.shards_of_rank(len(shards), rank, world)
+        lq = torch.empty(LB, LS, HQ, D, device=dev, dtype=torch.bfloat16)
+        lk = torch.empty(LB, LS, HKV, D, device=dev, dtype=torch.bfloat16)
+        lv, ldo = torch.empty_like(lk), torch.empty_like(lq)
+
+        def fill(ids):
+            for s_id in ids:
+                b, g = shards[s_id]
+                sg = torch.Generator(device=dev).manual_seed(5000 + s_id)
+                for t, h0, hn in ((lq, g * G, G), (lk, g, 1), (lv, g, 1), (ldo, g * G, G)):
+                    t[b, :, h0 : h0 + hn] = torch.randn(LS, hn, D, device=dev, generator=sg).to(torch.bfloat16)
+
+        def run_shards(ids, keep=None):
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            outs = []
+            for s_id in ids:
+                qs, ks, vs = sharding.shard_views(lq, lk, lv, shards[s_id], HQ, HKV)
+                outs.append((s_id,) + I._flash_attn_fwd(qs, ks, vs, causal=True, return_lse=True))
+            e[1].record()
+            for s_id, out, lse in outs:
+                b, g = shards[s_id]
+                qs, ks, vs = sharding.shard_views(lq, lk, lv, shards[s_id], HQ, HKV)
+                grads = I._flash_attn_bwd(qs, ks, vs, out, ldo[b : b + 1, :, g * G : (g + 1) * G], lse, causal=True)
+                if keep is not None:
+                    keep[s_id] = (out, lse) + tuple(grads)
+            e[2].record()
+            return e
+
+        fill(mine)
+        f_shard = 4.0 * G * LS * LS * D * 0.5
+        best = None
+        for it in range(3):
+            barrier()
+            e = run_shards(mine)
+            torch.cuda.synchronize(dev)
+            tf = sharding.max_over_ranks(e[0].elapsed_time(e[1]), dev)
+            tb = sharding.max_over_ranks(e[1].elapsed_time(e[2]), dev)
+            if it > 0 and (best is None or tf + tb < sum(best)):
+                best = (tf, tb)
+        # check: the last 1024 query rows of this rank's first shard against the oracle run on this GPU
+        # (out and dq of a row block need nothing but those rows; dk/dv parity at this size is in tests/)
+        from oracle import attention_oracle as O
+
+        local_err = {}
+        if mine:
+            kept = {}
+            run_shards(mine[:1], keep=kept)
+            s_id = mine[0]
+            b, g = shards[s_id]
+            out, lse, dq = kept[s_id][0], kept[s_id][1], kept[s_id][2]
+            r0 = LS - 1024
+            qs, ks, vs = sharding.shard_views(lq, lk, lv, shards[s_id], HQ, HKV)
+            scale = D ** -0.5
+            qf = qs[0, r0:].float()  # (R, G, D)
+            sc = torch.einsum("rgd,kd->grk", qf * scale, ks[0, :, 0].float())
+            hid = O._causal_mask(torch.arange(r0, LS, device=dev), LS, LS, dev)
+            sc = sc.masked_fill(hid[None], float("-inf"))
+            lref = torch.logsumexp(sc, -1)
+            pr = torch.exp(sc - lref[..., None])
+            oref = torch.einsum("grk,kd->rgd", pr, vs[0, :, 0].float())
+            dof = ldo[b, r0:, g * G : (g + 1) * G].float()
+            delta = (oref * dof).sum(-1).t()
+            dp = torch.einsum("rgd,kd->grk", dof, vs[0, :, 0].float())
+            dqref = torch.einsum("grk,kd->rgd", pr * (dp - delta[..., None]) * scale, ks[0, :, 0].float())
+            local_err[s_id] = max((out[0, r0:].float() - oref).abs().max().item(),
+                                  (dq[0, r0:].float() - dqref).abs().max().item(),
+                                  (lse[0, :, r0:] - lref).abs().max().item())
+            del kept, sc, pr, dp, hid
+        errs = sharding.gather_shard_results(local_err, len(shards), dev)
+        # the N = 1 time of the same work on this box: rank 0 runs all 8 shards by itself afterwards
+        t1 = None
+        barrier()
+        if rank == 0:
+            fill([i for i in range(len(shards)) if i not in mine])
+            b1 = None
+            for it in range(2):
+                e = run_shards(list(range(len(shards))))
+                torch.cuda.synchronize(dev)
+                b1 = (e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]))
+            t1 = b1
+        barrier()
+        if rank == 0:
+            tf, tb = best
+            n_sh = len(shards)
+            config5 = {"workload": "B=2 S=32768 Hq=32 Hkv=4 D=512 causal bf16, 8 (batch, kv-head group) shards round-robin over the ranks",
+                       "scaling": "strong", "shards_per_rank": len(mine), "fwd_ms": tf, "bwd_ms": tb,
+                       "fwd_tflops": n_sh * f_shard / tf / 1e9, "bwd_tflops": 2.5 * n_sh * f_shard / tb / 1e9,
+                       "fwd_frac_of_peak_per_gpu": n_sh * f_shard / tf / 1e9 / peak / world,
+                       "bwd_frac_of_peak_per_gpu": 2.5 * n_sh * f_shard / tb / 1e9 / peak / world,
+                       "n1_same_box": {"fwd_ms": t1[0], "bwd_ms": t1[1]},
+                       "speedup_vs_n1": (t1[0] + t1[1]) / (tf + tb),
+                       "check_max_abs_err_per_shard": [None if x == float("-inf") else x for x in errs],
+                       "check": "out, lse and dq of the last 1024 rows of each rank's first shard vs the fp32 oracle on the GPU"}
+        del lq, lk, lv, ldo
+        torch.cuda.empty_cache()
+
+    # ---- the packed causal training step (sequence lengths uniform in [128, 8192], 32768 tokens, seed 0), N = 1
     other = None
     if rank == 0 and world == 1 and not args.skip_e2e:
-        del q, k, v, do
-        torch.cuda.empty_cache()
         other = {}
-
-        def time_case(name, mk, hq, hkv, flops, **kw):
-            qq, kk, vv, dd = mk(hq), mk(hkv), mk(hkv), mk(hq)
-            res = []
-            for it in range(3):
-                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-                e0.record()
-                out, lse = I._flash_attn_fwd(qq, kk, vv, causal=True, return_lse=True, **kw)
-                e1.record()
-                I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=True, **kw)
-                e2.record()
-                torch.cuda.synchronize(dev)
-                res.append((e0.elapsed_time(e1), e1.elapsed_time(e2)))
-            tf, tb = min(r[0] for r in res[1:]), min(r[1] for r in res[1:])
-            other[name] = {"fwd_ms": tf, "bwd_ms": tb, "fwd_tflops": flops / tf / 1e9, "bwd_tflops": 2.5 * flops / tb / 1e9}
-
         gen, lens = torch.Generator().manual_seed(0), []
         while sum(lens) < 32768:
             lens.append(int(torch.randint(128, 8193, (1,), generator=gen)))
         lens[-1] -= sum(lens) - 32768
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
-        time_case("packed_causal_32768_tokens", lambda h: torch.randn(32768, h, D, device=dev).to(torch.bfloat16),
-                  HQ, HKV, sum(4.0 * HQ * n * n * D for n in lens) * 0.5,
-                  cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
-        other["packed_causal_32768_tokens"]["sequence_lengths"] = lens
-        time_case("shard_B1_S32768_Hq8_Hkv1_causal", lambda h: torch.randn(1, 32768, h, D, device=dev).to(torch.bfloat16),
-                  8, 1, 4.0 * 8 * 32768 * 32768 * D * 0.5)
+        mkp = lambda h: torch.randn(32768, h, D, device=dev).to(torch.bfloat16)
+        pq, pk, pv, pdo = mkp(HQ), mkp(HKV), mkp(HKV), mkp(HQ)
+        kw = dict(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+        ts = timed(lambda: fwd_bwd_events(pq, pk, pv, pdo, True, **kw))
+        fl = sum(4.0 * HQ * n * n * D for n in lens) * 0.5
+        tb = sum(v for kk_, v in ts.items() if kk_ != "fwd")
+        other["packed_causal_32768_tokens"] = {"fwd_ms": ts["fwd"], "bwd_ms": tb, "fwd_tflops": fl / ts["fwd"] / 1e9,
+                                               "bwd_tflops": 2.5 * fl / tb / 1e9, "sequence_lengths": lens}
+        del pq, pk, pv, pdo
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.skip_e2e:
-        fl, dt = cpu_sample()
+        cpu_sample()  # warm-up: thread pool, allocator
+        fl, dt = cpu_sample(repeat=3)
         cpu_baseline = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                        "sample": "fp32 fwd+bwd of B=1,S=1024,Hq=32,Hkv=4,D=512, causal and non-causal, once (oracle port of the reference's PyTorch attention)"}
+                        "sample": "fp32 fwd+bwd of B=1,S=1024,Hq=32,Hkv=4,D=512, causal and non-causal, 3 passes after one warm-up pass (oracle port of the reference's PyTorch attention)"}
 
     if rank == 0:
         line = {
@@ -373,19 +521,73 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "fwd+bwd sweep: Hq=32 Hkv=4 D=512, (B,S) in (16,1024),(8,2048),(4,4096),(2,8192),(1,16384), causal and non-causal",
-                       "l2": "operands of every shape (1.2 GB) exceed the 126 MB L2", "per_rank": "same sweep, own seed"},
+                       "l2": "operands of every shape (1.2 GB) exceed the 126 MB L2", "per_rank": "same sweep, own seed",
+                       "also": "config5 = the B=2 S=32768 layer as 8 shards over the ranks (strong scaling)"},
             "fwd_tflops": fwd_tflops, "bwd_tflops": bwd_tflops,
             "fwd_frac_of_peak": fwd_tflops / peak, "bwd_frac_of_peak": bwd_tflops / peak,
             "frac_of_nominal_2250": {"fwd": fwd_tflops / 2250.0, "bwd": bwd_tflops / 2250.0},
             "frac_of_sustained": {"fwd": fwd_tflops / peak_sus, "bwd": bwd_tflops / peak_sus},
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": launches, "clocks": clocks.summary(), "sweep": sweep, "other_configs": other,
+            "gpu_launches": launches, "clocks": clocks.summary(), "sweep": sweep + fp16_rows, "config5": config5,
+            "other_configs": other,
             "context_sm90_readme": {"fwd_tflops": 270, "bwd_tflops": 100},
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_case(args):
+    """One shape, per-kernel CUDA-event times, as text (the command to put under ncu)."""
+    from splitd_flash_attn import interface as I
+
+    spec = args.case.split(",")
+    causal = "causal" in spec[1:] or "1" in spec[2:]
+    hq, hkv = (int(x) for x in args.heads.split(","))
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    kw = {}
+    if spec[0].startswith("packed:"):
+        total = int(spec[0].split(":")[1])
+        gen, lens = torch.Generator().manual_seed(0), []
+        while sum(lens) < total:
+            lens.append(int(torch.randint(128, 8193, (1,), generator=gen)))
+        lens[-1] -= sum(lens) - total
+        print("sequence lengths:", lens)
+        mk = lambda h: torch.randn(total, h, D, device=dev).to(torch.bfloat16)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        kw = dict(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+        F = sum(4.0 * hq * n * n * D for n in lens) * (0.5 if causal else 1.0)
+    else:
+        B, S = int(spec[0]), int(spec[1])
+        mk = lambda h: torch.randn(B, S, h, D, device=dev).to(torch.bfloat16)
+        F = 4.0 * B * hq * S * S * D * (0.5 if causal else 1.0)
+    q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+    for it in range(args.iters):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out, lse = I._flash_attn_fwd(q, k, v, causal=causal, return_lse=True, **kw)
+        evs = [("fwd", e0)]
+        if args.no_backward:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            evs.append(("end", e1))
+        else:
+            I._flash_attn_bwd(q, k, v, out, do, lse, causal=causal, stage_events=evs, **kw)
+        torch.cuda.synchronize()
+        ts = {}
+        for (label, ev), (_, nxt) in zip(evs[:-1], evs[1:]):
+            ts[label] = ts.get(label, 0.0) + ev.elapsed_time(nxt)
+        line = f"iter {it}: fwd {ts['fwd']:.3f} ms ({F / ts['fwd'] / 1e9:.0f} TFLOP/s)"
+        if not args.no_backward:
+            tb = sum(t for n, t in ts.items() if n != "fwd")
+            line += (f" | preprocess {ts['bwd_preprocess']:.3f} ms | P/dS tiles {ts['bwd_tiles']:.3f} ms "
+                     f"({F / ts['bwd_tiles'] / 1e9:.0f}) | dQ+dK+dV GEMMs {ts['bwd_grads']:.3f} ms "
+                     f"({1.5 * F / ts['bwd_grads'] / 1e9:.0f}) | bwd {tb:.3f} ms ({2.5 * F / tb / 1e9:.0f} TFLOP/s)"
+                     f" | chunks {sum(1 for n, _ in evs if n == 'bwd_tiles')}")
+        print(line)
+    print("status", I.kernel_status())
 
 
 def main():
@@ -395,8 +597,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true", help="profiling aid: leave out the host-buffer end-to-end leg")
+    ap.add_argument("--case", default="", help="time one shape per kernel and print text: B,S[,causal] or packed:T[,causal]")
+    ap.add_argument("--iters", type=int, default=3, help="--case: repetitions")
+    ap.add_argument("--heads", default="32,4", help="--case: query heads, kv heads")
+    ap.add_argument("--no-backward", action="store_true", help="--case: forward only")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -577,7 +577,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (p.softcap_pre != 0.f) {
           // softcap: s <- tanh(s * scale / softcap); scale_log2 then holds softcap * log2(e)
 #pragma unroll
-          for (int i = 0; i < 64; ++i) r[i] = __float_as_uint(tanh_approx(__uint_as_float(r[i]) * p.softcap_pre));
+          for (int i = 0; i < 64; ++i) r[i] = __float_as_uint(tanh_precise(__uint_as_float(r[i]) * p.softcap_pre));
         }
         if (cl < 63) {
 #pragma unroll

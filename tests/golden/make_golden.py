@@ -13,6 +13,9 @@ Cases
   cfg1      : the CPU plumbing configuration -- B=1, S=256, Hq=8, Hkv=1, fp32 N(0,1) inputs, seed 0, non-causal
   gqa_causal: B=2, Sq=113, Sk=203, Hq=4, Hkv=2, causal (bottom-right aligned), seed 42
   mha_tail  : B=1, Sq=64,  Sk=128, Hq=2, Hkv=2, causal, seed 7
+  cfg1_bf16, gqa_causal_bf16: the same two cases with q, k, v and dO rounded to bfloat16 first (still computed in
+              fp32 by the reference): the inputs a 16-bit kernel can be given exactly, so its outputs can be
+              compared with these vectors under the 2 x yardstick rule
 Outputs: out, lse (logsumexp of masked scaled scores, test :562-571), dq, dk, dv from autograd.
 Only a strided subsample of each output is stored to keep the files a few hundred KB.
 """
@@ -27,6 +30,8 @@ CASES = {
     "cfg1": dict(B=1, sq=256, sk=256, hq=8, hkv=1, causal=False, seed=0),
     "gqa_causal": dict(B=2, sq=113, sk=203, hq=4, hkv=2, causal=True, seed=42),
     "mha_tail": dict(B=1, sq=64, sk=128, hq=2, hkv=2, causal=True, seed=7),
+    "cfg1_bf16": dict(B=1, sq=256, sk=256, hq=8, hkv=1, causal=False, seed=0, bf16_inputs=True),
+    "gqa_causal_bf16": dict(B=2, sq=113, sk=203, hq=4, hkv=2, causal=True, seed=42, bf16_inputs=True),
 }
 D = 512
 
@@ -37,6 +42,8 @@ def make_inputs(c):
     k = torch.randn(c["B"], c["sk"], c["hkv"], D, generator=gen)
     v = torch.randn(c["B"], c["sk"], c["hkv"], D, generator=gen)
     do = torch.randn(c["B"], c["sq"], c["hq"], D, generator=gen)
+    if c.get("bf16_inputs"):
+        q, k, v, do = (t.to(torch.bfloat16).float() for t in (q, k, v, do))
     return q, k, v, do
 
 
@@ -71,7 +78,8 @@ def main(ref_root):
             dq=subsample(dq),
             dk=subsample(dk),
             dv=subsample(dv),
-            meta=np.array([c["B"], c["sq"], c["sk"], c["hq"], c["hkv"], int(c["causal"]), c["seed"]], dtype=np.int64),
+            meta=np.array([c["B"], c["sq"], c["sk"], c["hq"], c["hkv"], int(c["causal"]), c["seed"],
+                           int(c.get("bf16_inputs", False))], dtype=np.int64),
         )
         print(name, "written")
 

@@ -104,6 +104,13 @@ def sdpa_math(q, k, v, causal=False, scale=None, window=(None, None), do=None):
     return (out, dq, dk, dv) if want_grad else out
 
 
+def rounding_yardstick(ref, dtype):
+    """Error of the exact result rounded once to `dtype`. For 16-bit inputs the math backend computes in fp32
+    and rounds its results once, so this IS its error (measured: identical for out and dq, and for dk/dv of
+    MHA); used where SDPA cannot express the case (softcap, a gradient flowing into lse)."""
+    return max_err(ref.to(dtype), ref)
+
+
 def _report(name, err, yard, loose=None):
     extra = "" if loose is None else f", 16-bit-matmul restatement {loose:.3e}"
     print(f"    {name}: err {err:.3e} = {err / max(yard, 1e-30):.2f} x SDPA-MATH yardstick {yard:.3e}{extra}")
@@ -148,6 +155,40 @@ def check_all(out, lse, dq, dk, dv, q, k, v, do, causal, scale=None):
     """Forward + backward acceptance on one (B, S, H, D) problem small enough for the oracle."""
     check_fwd(out, lse, q, k, v, causal, scale)
     return check_bwd(dq, dk, dv, q, k, v, do, causal, scale)
+
+
+def check_varlen(out, lse, grads, q, k, v, do, cu_q, cu_k, causal, scale=None, heads=None):
+    """Packed layout: oracle and yardstick per sequence (that is what the packed call computes), errors and
+    yardsticks taken over the whole packed tensors. `heads` = (query-head slice, kv-head slice) restricts the
+    check to some heads of a large problem. `grads` = (dq, dk, dv) or None."""
+    hs_q, hs_k = heads if heads is not None else (slice(None), slice(None))
+    names = ("out", "dq", "dk", "dv") if grads is not None else ("out",)
+    errs = dict.fromkeys(names, 0.0)
+    yards = dict.fromkeys(names, 0.0)
+    for b in range(len(cu_q) - 1):
+        qs, qe, ks, ke = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
+        if qe == qs:
+            continue
+        qb, kb, vb = q.detach()[None, qs:qe, hs_q], k.detach()[None, ks:ke, hs_k], v.detach()[None, ks:ke, hs_k]
+        ro, rl = O.attention_fwd(qb, kb, vb, causal, scale)
+        check_lse(lse[hs_q, qs:qe][None], rl)
+        got = {"out": out[None, qs:qe, hs_q]}
+        ref = {"out": ro}
+        if grads is not None and ke > ks:
+            dob = do[None, qs:qe, hs_q]
+            ref["dq"], ref["dk"], ref["dv"] = O.attention_bwd(qb, kb, vb, dob, causal, scale)
+            yo, yq, yk, yv = sdpa_math(qb, kb, vb, causal, scale, do=dob)
+            yd = {"out": yo, "dq": yq, "dk": yk, "dv": yv}
+            got["dq"], got["dk"], got["dv"] = grads[0][None, qs:qe, hs_q], grads[1][None, ks:ke, hs_k], grads[2][None, ks:ke, hs_k]
+        else:
+            yd = {"out": sdpa_math(qb, kb, vb, causal, scale)}
+        for n in got:
+            assert not torch.isnan(got[n]).any(), n
+            errs[n] = max(errs[n], max_err(got[n], ref[n]))
+            yards[n] = max(yards[n], max_err(yd[n], ref[n]))
+    for n in names:
+        _report(n, errs[n], yards[n])
+        assert errs[n] <= ERR_FACTOR * yards[n] + ATOL, f"{n} err {errs[n]:.3e} > {ERR_FACTOR} x yardstick {yards[n]:.3e}"
 
 
 def assert_status_ok():

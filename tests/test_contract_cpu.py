@@ -78,3 +78,51 @@ def test_varlen_custom_op_traces_under_fake_tensors():
         )
         assert gq.shape == q.shape and gk.shape == kv.shape and gv.shape == kv.shape
     assert hasattr(torch.ops.splitd_flash_attn, "varlen_fwd") and hasattr(torch.ops.splitd_flash_attn, "varlen_bwd")
+
+
+def test_batched_custom_op_traces_under_fake_tensors():
+    """The batched layout goes through a custom op pair of its own (splitd_flash_attn::fwd / ::bwd) with fake
+    kernels, so it is traceable without a GPU like the packed one."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from splitd_flash_attn import split_flash_attn_func
+
+    with FakeTensorMode():
+        q = torch.empty(2, 96, 8, D, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        kv = torch.empty(2, 80, 2, D, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        out, lse = split_flash_attn_func(q, kv, kv, causal=True, return_lse=True)
+        assert out.shape == (2, 96, 8, D) and out.dtype == torch.bfloat16
+        assert lse.shape == (2, 8, 96) and lse.dtype == torch.float32
+        gq, gk, gv = torch.ops.splitd_flash_attn.bwd(
+            q.detach(), kv.detach(), kv.detach(), out.detach(), out.detach(), lse, 0.05, True, -(2**31), -(2**31), 0.0, None
+        )
+        assert gq.shape == q.shape and gk.shape == kv.shape and gv.shape == kv.shape
+        q16 = torch.empty(2, 96, 8, D, dtype=torch.float16, device="cuda", requires_grad=True)
+        with pytest.raises(NotImplementedError, match="bfloat16 only"):
+            split_flash_attn_func(q16, q16, q16)
+    assert hasattr(torch.ops.splitd_flash_attn, "fwd") and hasattr(torch.ops.splitd_flash_attn, "bwd")
+
+
+def test_backward_workspace_is_bounded_for_the_full_layer():
+    """Sizing needs no GPU. The B=2, S=32768, Hq=32, Hkv=4 layer would need 275 GB for all of its P / dS tiles;
+    the default workspace caps the tiles at 6 GiB and the smallest accepted one is the operand copies plus a
+    few tiles. Whatever lies between is accepted, and more memory never means more chunks."""
+    import ctypes
+
+    from splitd_flash_attn import _capi
+
+    lib = _capi.load_library()
+    p = _capi.SplitdParams()
+    p.batch, p.seqlen_q, p.seqlen_k, p.heads_q, p.heads_kv, p.head_dim = 2, 32768, 32768, 32, 4, 512
+    everything = lib.splitd_bwd_workspace_bytes_limit(ctypes.byref(p), ctypes.c_size_t(-1).value)
+    default = lib.splitd_bwd_workspace_bytes(ctypes.byref(p))
+    smallest = lib.splitd_bwd_workspace_bytes_limit(ctypes.byref(p), 0)
+    copies = (2 * 2 * 32768 * 32 + 2 * 32768 * 4) * 512 * 2
+    assert everything > 270e9
+    assert copies < smallest < copies + (1 << 30)
+    assert smallest < default < copies + (8 << 30)
+    # the sweep's shapes fit the default without row splitting: whole KV heads or everything at once
+    p.batch, p.seqlen_q, p.seqlen_k = 16, 1024, 1024
+    assert lib.splitd_bwd_workspace_bytes(ctypes.byref(p)) == lib.splitd_bwd_workspace_bytes_limit(
+        ctypes.byref(p), ctypes.c_size_t(-1).value
+    )

@@ -13,16 +13,18 @@ D = 512
 
 
 def _inputs(meta):
-    B, sq, sk, hq, hkv, causal, seed = (int(x) for x in meta)
+    B, sq, sk, hq, hkv, causal, seed, bf16_inputs = (int(x) for x in meta)
     gen = torch.Generator().manual_seed(seed)
     q = torch.randn(B, sq, hq, D, generator=gen)
     k = torch.randn(B, sk, hkv, D, generator=gen)
     v = torch.randn(B, sk, hkv, D, generator=gen)
     do = torch.randn(B, sq, hq, D, generator=gen)
+    if bf16_inputs:
+        q, k, v, do = (t.to(torch.bfloat16).float() for t in (q, k, v, do))
     return q, k, v, do, bool(causal)
 
 
-@pytest.mark.parametrize("name", ["cfg1", "gqa_causal", "mha_tail"])
+@pytest.mark.parametrize("name", ["cfg1", "gqa_causal", "mha_tail", "cfg1_bf16", "gqa_causal_bf16"])
 def test_oracle_matches_reference_golden(name):
     g = np.load(os.path.join(GOLDEN, f"{name}.npz"))
     q, k, v, do, causal = _inputs(g["meta"])
