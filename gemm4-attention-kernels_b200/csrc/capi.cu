@@ -178,6 +178,8 @@ int splitd_fwd(const splitd_params* p, void* stream) {
   return launch_fwd(p, static_cast<cudaStream_t>(stream));
 }
 
+size_t splitd_fwd_workspace_bytes(const splitd_params* p) { return p ? fwd_workspace_bytes(p) : 0; }
+
 size_t splitd_bwd_rowstat_elems(const splitd_params* p) { return p ? bwd_rowstat_elems(p) : 0; }
 size_t splitd_bwd_workspace_bytes(const splitd_params* p) { return p ? bwd_workspace_bytes(p) : 0; }
 size_t splitd_bwd_workspace_bytes_limit(const splitd_params* p, size_t tile_bytes_limit) {

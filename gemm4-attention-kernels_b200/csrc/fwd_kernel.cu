@@ -12,8 +12,11 @@
 // the issuing warp keeps up: see the MMA issuer below.)
 //
 // Per KV step of 256 keys:  S = Q K^T (32 MMAs, K-major operands)  ->  softmax warps: row max
-// (exchanged between the four threads that share a row), P = exp2(...) as bf16 into shared memory
-// -> O += P V (32 MMAs, V as MN-major B operand).  S is double buffered so the tensor pipe runs
+// (exchanged between the four threads that share a row), P = exp2(...) as fp16 into shared memory
+// -> O += P V (32 MMAs, V as MN-major B operand). P is fp16 for bf16 inputs too: with bf16's 8 significant
+// bits the rounding of P alone puts a non-causal output at up to twice the error of a result that is rounded
+// once; fp16 has 11. The two operands of an MMA must share a format, so for bf16 inputs V is read from an fp16
+// copy that a small kernel makes in the caller's workspace right before (K/V are the small tensors of GQA).  S is double buffered so the tensor pipe runs
 // S(j+1) while the softmax warps work on S(j).  O is only rescaled when a row max grows by more
 // than 2^8 (the exact value is restored by the final 1/rowsum scaling).
 //
@@ -34,6 +37,7 @@
 #include "common.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
+#include "rowcopy.cuh"
 
 namespace sd {
 
@@ -310,7 +314,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // barrier wait / commit covers 8 MMAs (a 32 KB stage).
     if (rank == 0) {
       constexpr uint32_t idesc_s = make_idesc(kFp16, false, false, 128, kStepKeys);
-      constexpr uint32_t idesc_pv = make_idesc(kFp16, false, true, 128, 256);
+      constexpr uint32_t idesc_pv = make_idesc(true, false, true, 128, 256);  // P and V (copy) are fp16 always
       const uint32_t p_lo = desc_lo(sP, 16);
       uint32_t it = 0;     // ring acquisitions consumed
       uint32_t gs = 0;     // KV steps issued so far (S buffer / barrier phase index)
@@ -625,7 +629,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float a = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, -ms));
           const float b = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -ms));
           l_sum += a + b;
-          r[i >> 1] = pack2<kFp16>(a, b);
+          r[i >> 1] = pack_half2(a, b);  // <= 2^8 by the rescale rule
         }
 
         if (prof) { const long long q1 = clock64(); tph3 += q1 - q0; q0 = q1; }
@@ -720,6 +724,28 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 }
 
+// V (any supported strides) -> contiguous fp16 (B,Sk,Hkv,512) / (Tk,Hkv,512); one warp per (token, head) row.
+// Values beyond fp16's range saturate and |v| < 2^-14 loses bits to subnormals; attention values of ordinary
+// magnitude are far from both.
+__global__ void __launch_bounds__(256) splitd_fwd_vcopy_kernel(const uint16_t* v, uint16_t* v_h, int64_t n_rows,
+                                                               int heads_kv, int tokens_per_batch, int64_t stride_b,
+                                                               int64_t stride_s, int64_t stride_h) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int h = static_cast<int>(row % heads_kv);
+  const int64_t tok = row / heads_kv;
+  const int64_t b = tok / tokens_per_batch, s = tok - b * tokens_per_batch;
+  store_row_half(v_h + row * kHeadDim, lane, load_row(v + b * stride_b + s * stride_s + h * stride_h, lane), 1.f);
+}
+
+size_t fwd_workspace_bytes(const splitd_params* p) {
+  if (p->dtype == SPLITD_DTYPE_FP16) return 0;
+  const bool varlen = p->cu_seqlens_k != nullptr;
+  const int64_t tok = varlen ? p->total_k : static_cast<int64_t>(p->batch) * p->seqlen_k;
+  return static_cast<size_t>((tok * p->heads_kv * kHeadDim * 2 + 255) / 256 * 256);
+}
+
 int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   FwdParams fp;
   memset(&fp, 0, sizeof(fp));
@@ -728,7 +754,29 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   CUtensorMap tm_q, tm_k, tm_v;
   if (int e = make_q_tmap(&tm_q, p->q, p, g, p->q_strides, g.pos_per_cta, "q")) return e;
   if (int e = make_kv_tmap(&tm_k, p->k, p, p->k_strides, 128, "k")) return e;
-  if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 64, "v")) return e;
+  const bool varlen_k = p->cu_seqlens_k != nullptr;
+  if (p->dtype == SPLITD_DTYPE_FP16) {
+    if (int e = make_kv_tmap(&tm_v, p->v, p, p->v_strides, 64, "v")) return e;
+  } else {
+    const size_t need = fwd_workspace_bytes(p);
+    if (!p->workspace || p->workspace_bytes < need)
+      return fail(SPLITD_ERR_WORKSPACE, "forward with bf16 inputs needs a workspace of %zu bytes (splitd_fwd_workspace_bytes), got %zu",
+                  need, p->workspace ? p->workspace_bytes : static_cast<size_t>(0));
+    if (reinterpret_cast<uintptr_t>(p->workspace) % 256 != 0 || reinterpret_cast<uintptr_t>(p->v) % 16 != 0)
+      return fail(SPLITD_ERR_WORKSPACE, "workspace must be 256-byte aligned and v 16-byte aligned");
+    for (int i = 0; i < 3; ++i)
+      if (p->v_strides[i] % 8 != 0) return fail(SPLITD_ERR_INVALID_ARGUMENT, "v strides must be multiples of 8 elements");
+    const int64_t sk = varlen_k ? p->total_k : p->seqlen_k;
+    const int64_t n_rows = (varlen_k ? 1 : static_cast<int64_t>(p->batch)) * sk * p->heads_kv;
+    const int64_t blocks = (n_rows + 7) / 8;
+    if (blocks <= 0 || blocks > 0x7fffffffll) return fail(SPLITD_ERR_INVALID_ARGUMENT, "V copy grid out of range");
+    uint16_t* v_h = static_cast<uint16_t*>(p->workspace);
+    splitd_fwd_vcopy_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const uint16_t*>(p->v), v_h, n_rows, p->heads_kv, static_cast<int>(sk), varlen_k ? 0 : p->v_strides[0],
+        p->v_strides[1], p->v_strides[2]);
+    const int64_t vs[3] = {sk * p->heads_kv * kHeadDim, static_cast<int64_t>(p->heads_kv) * kHeadDim, kHeadDim};
+    if (int e = make_kv_tmap(&tm_v, v_h, p, vs, 64, "v (fp16 copy)")) return e;
+  }
   if (reinterpret_cast<uintptr_t>(p->o) % 16 != 0 || p->o_strides[1] % 8 != 0 || p->o_strides[2] % 8 != 0 ||
       p->o_strides[0] % 8 != 0)
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "o must be 16-byte aligned with strides that are multiples of 8 elements");

@@ -39,9 +39,10 @@ struct BwdPlan {
   int64_t tiles_per_chunk;
 };
 // planes of at most this many bytes by default (splitd_bwd_workspace_bytes); the caller may give more or less
-constexpr size_t kDefaultPlaneLimit = static_cast<size_t>(6) << 30;
+constexpr size_t kDefaultPlaneLimit = static_cast<size_t>(9) << 30;
 
 int launch_fwd(const splitd_params* p, cudaStream_t stream);
+size_t fwd_workspace_bytes(const splitd_params* p);
 int launch_bwd_preprocess(const splitd_params* p, cudaStream_t stream);
 // stages: bit 0 = P / dS tiles of chunk `chunk`, bit 1 = dK and dV, bit 2 = dQ from them
 int launch_bwd_chunk(const splitd_params* p, const BwdPlan& pl, int chunk, int stages, cudaStream_t stream);

@@ -19,6 +19,7 @@ SPLITD_DTYPE_FP16 = 1
 EXPORTED_SYMBOLS = (
     "splitd_device_supported",
     "splitd_fwd",
+    "splitd_fwd_workspace_bytes",
     "splitd_bwd_rowstat_elems",
     "splitd_bwd_workspace_bytes",
     "splitd_bwd_workspace_bytes_limit",
@@ -125,7 +126,7 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [pp, ctypes.c_void_p]
         fn.restype = ctypes.c_int
-    for name in ("splitd_bwd_rowstat_elems", "splitd_bwd_workspace_bytes"):
+    for name in ("splitd_fwd_workspace_bytes", "splitd_bwd_rowstat_elems", "splitd_bwd_workspace_bytes"):
         fn = getattr(lib, name)
         fn.argtypes = [pp]
         fn.restype = ctypes.c_size_t

@@ -56,7 +56,7 @@ def cu_seqlens_validation(enabled: bool):
         _VALIDATE_CU_SEQLENS = old
 
 
-# Cap on the bytes of P / dS tiles the backward keeps in memory at once (None: the library's default, 6 GiB).
+# Cap on the bytes of P / dS tiles the backward keeps in memory at once (None: the library's default, 9 GiB).
 # Larger problems are processed in chunks that reuse the same memory; results do not depend on it.
 _env_limit = os.environ.get("SPLITD_BWD_WORKSPACE_LIMIT_BYTES")
 _WORKSPACE_LIMIT: Optional[int] = int(_env_limit) if _env_limit else None
@@ -433,8 +433,13 @@ def _flash_attn_fwd(
         params.local = 1
         params.window_left = -1 if window_size_left is None or window_size_left < 0 else int(window_size_left)
         params.window_right = -1 if window_size_right is None or window_size_right < 0 else int(window_size_right)
+    lib = _capi.load_library()
+    n_ws = lib.splitd_fwd_workspace_bytes(ctypes.byref(params))  # fp16 copy of v (bf16 inputs only)
+    if n_ws:
+        workspace = torch.empty(n_ws, dtype=torch.uint8, device=device)
+        params.workspace, params.workspace_bytes = _ptr(workspace), n_ws
     with torch.cuda.device(device):
-        _capi.check(_capi.load_library().splitd_fwd(ctypes.byref(params), _stream_ptr(device)))
+        _capi.check(lib.splitd_fwd(ctypes.byref(params), _stream_ptr(device)))
     return out, lse
 
 

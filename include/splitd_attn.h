@@ -57,7 +57,8 @@ typedef struct {
   void* dv;          /* like v                                                    */
   float* dpsum;      /* fp32 scratch, splitd_bwd_rowstat_elems() elements          */
   float* lse_log2;   /* fp32 scratch, same size                                   */
-  void* workspace;   /* scratch for the P / dS tiles (fp16), 256-byte aligned; see splitd_bwd_workspace_bytes() */
+  void* workspace;   /* scratch, 256-byte aligned: forward, splitd_fwd_workspace_bytes(); backward (P / dS tiles
+                        and fp16 operand copies), splitd_bwd_workspace_bytes()                              */
   size_t workspace_bytes; /* how much of it the library may use                    */
 
   /* ---- packed (varlen) layout; both NULL selects the batched layout ---- */
@@ -106,8 +107,12 @@ int splitd_device_supported(int device);
 
 /* Forward: o = softmax(q k^T * scale [+ causal mask]) v, lse = logsumexp of the scaled scores.
  * Replaces the compiled forward call `compile_cache[key](q,k,v,out,lse,scale,cu_q,cu_k,...)`
- * (src/interface.py:538-553, kernel src/flash_fwd_sm90_d512.py). bf16 or fp16. */
+ * (src/interface.py:538-553, kernel src/flash_fwd_sm90_d512.py). bf16 or fp16.
+ * With bf16 inputs the probabilities go to the tensor cores as fp16 (three more significant bits than bf16),
+ * which needs v in fp16 too: the call first copies v into `workspace` (splitd_fwd_workspace_bytes(p) bytes,
+ * the size of v, 256-byte aligned; `workspace_bytes` says how much is there). fp16 inputs need no workspace. */
 int splitd_fwd(const splitd_params* p, void* stream);
+size_t splitd_fwd_workspace_bytes(const splitd_params* p);
 
 /* Number of fp32 elements the caller must provide in each of `dpsum` and `lse_log2`: one per (query row,
  * query head), batch * heads_q * seqlen_q or heads_q * total_q, no padding (src/interface.py:747-753 pads the
@@ -121,7 +126,8 @@ size_t splitd_bwd_rowstat_elems(const splitd_params* p);
  * or, when one KV head of one batch is still too large, of row ranges whose dK/dV partial sums travel from chunk to chunk
  * in fp32, and reuses the same tile memory for every chunk. Results do not depend on the chunking, bit for bit.
  *   splitd_bwd_workspace_bytes(p)            what to allocate by default: everything at once if the tiles take at
- *                                            most 6 GiB, else 6 GiB of tiles plus the fixed parts;
+ *                                            most 9 GiB, else up to 9 GiB of tiles plus the fixed parts (measured: whole-KV-head chunks of that
+ *                                            size cost nothing, much smaller ones up to 10 %);
  *   splitd_bwd_workspace_bytes_limit(p, n)   the same with your own cap n on the tile bytes; n = 0 gives the
  *                                            smallest workspace splitd_bwd accepts, n = SIZE_MAX the size that
  *                                            holds the whole problem in one chunk.

@@ -105,7 +105,7 @@ def test_batched_custom_op_traces_under_fake_tensors():
 
 def test_backward_workspace_is_bounded_for_the_full_layer():
     """Sizing needs no GPU. The B=2, S=32768, Hq=32, Hkv=4 layer would need 275 GB for all of its P / dS tiles;
-    the default workspace caps the tiles at 6 GiB and the smallest accepted one is the operand copies plus a
+    the default workspace caps the tiles at 9 GiB and the smallest accepted one is the operand copies plus a
     few tiles. Whatever lies between is accepted, and more memory never means more chunks."""
     import ctypes
 
@@ -120,7 +120,7 @@ def test_backward_workspace_is_bounded_for_the_full_layer():
     copies = (2 * 2 * 32768 * 32 + 2 * 32768 * 4) * 512 * 2
     assert everything > 270e9
     assert copies < smallest < copies + (1 << 30)
-    assert smallest < default < copies + (8 << 30)
+    assert smallest < default < copies + (11 << 30)
     # the sweep's shapes fit the default without row splitting: whole KV heads or everything at once
     p.batch, p.seqlen_q, p.seqlen_k = 16, 1024, 1024
     assert lib.splitd_bwd_workspace_bytes(ctypes.byref(p)) == lib.splitd_bwd_workspace_bytes_limit(
