@@ -172,11 +172,14 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's version banner,
+    # its INFO lines when the caller asks for them with NCCL_DEBUG) is sent to stderr by pointing file
+    # descriptor 1 at stderr; the JSON line goes to a private copy of the original stdout at the end.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if world > 1:
-        # stdout carries the one JSON line only: NCCL's own output (its version banner is printed from level
-        # WARN up) goes to stderr
         os.environ.setdefault("NCCL_DEBUG", "WARN")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -533,7 +536,8 @@ def run_ours(args):
             "other_configs": other,
             "context_sm90_readme": {"fwd_tflops": 270, "bwd_tflops": 100},
         }
-        print(json.dumps(line))
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
     if world > 1:
         dist.destroy_process_group()
 
