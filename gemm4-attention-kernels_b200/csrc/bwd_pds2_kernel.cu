@@ -34,10 +34,7 @@ namespace sd {
 
 namespace pds2 {
 constexpr int kStepKeys = 256;
-#ifndef SPLITD_PDS_CHUNK
-#define SPLITD_PDS_CHUNK 4
-#endif
-constexpr int kChunkSteps = SPLITD_PDS_CHUNK;  // key steps per pass before the pair switches to the other pass
+constexpr int kChunkSteps = 4;       // key steps per pass before the pair switches to the other pass (8, 16: +-2 %)
 constexpr int kStages = 6;
 constexpr int kStageBytes = 16384;   // this CTA's 128 keys x 64 of the 512 D columns
 constexpr int kABlockBytes = 16384;  // the tile's 128 rows x the same 64 D columns
@@ -117,21 +114,6 @@ __device__ __forceinline__ bool pds2_decode(const BwdParams& p, int ppu, int idx
   return true;
 }
 
-// 16-byte forms: a warp instruction of these touches 4 whole 128-byte lines when 8 consecutive lanes share a line
-__device__ __forceinline__ void ld_global_v4_hint(const void* p, uint32_t* w, uint64_t policy) {
-  asm volatile("ld.global.L2::cache_hint.v4.b32 {%0, %1, %2, %3}, [%4], %5;"
-               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-               : "l"(p), "l"(policy)
-               : "memory");
-}
-__device__ __forceinline__ void st_global_v4_hint(void* p, const uint32_t* w, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-               "r"(w[3]), "l"(policy)
-               : "memory");
-}
-#ifndef SPLITD_PDS_V4
-#define SPLITD_PDS_V4 0
-#endif
 __device__ __forceinline__ void ld_global_v8_hint(const void* p, uint32_t* w, uint64_t policy) {
   asm volatile("ld.global.L2::cache_hint.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8], %9;"
                : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
@@ -362,11 +344,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       uint16_t* ws_row = p.ws + (static_cast<int64_t>(t.hu - p.c_hu0) * 2) * plane +
                          (chunk_ws_row(p, t.tile_base, min(rt, t.n_row_tiles - 1)) + L) * p.ws_pitch;
       // after the 4 x 4 chunk transposes a thread handles chunk (lane & 3) of rows (lane & ~3) + r, r = 0..3
-#if SPLITD_PDS_V4
-      const int64_t row_delta0 = static_cast<int64_t>((lane & ~7) - lane) * p.ws_pitch;
-#else
       const int64_t row_delta0 = static_cast<int64_t>((lane & ~3) - lane) * p.ws_pitch;
-#endif
 
       // pass 1: the P values of a step come back with the access pattern of the stores (lane l reads 32-byte
       // chunk l & 3 of rows (l & ~3) + r: whole 128-byte lines per instruction, a quarter of the L1 wavefronts
@@ -376,17 +354,6 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // the step.
       uint32_t pq[64];
       auto load_p_half = [&](int step, int h2) {
-#if SPLITD_PDS_V4
-        const uint16_t* src = ws_row + row_delta0 + step * kStepKeys + ch * 128 + h2 * 64 + (lane & 7) * 8;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (tile_valid)
-            ld_global_v4_hint(src + r * p.ws_pitch, &pq[h2 * 32 + 4 * r], pol_stream);  // read once: may go now
-          else
-#pragma unroll
-            for (int i = 0; i < 4; ++i) pq[h2 * 32 + 4 * r + i] = 0u;
-        }
-#else
         const uint16_t* src = ws_row + row_delta0 + step * kStepKeys + ch * 128 + h2 * 64 + (lane & 3) * 16;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
@@ -396,7 +363,6 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
             for (int i = 0; i < 8; ++i) pq[h2 * 32 + 8 * r + i] = 0u;
         }
-#endif
       };
       for (int c0 = 0; c0 < t.n_steps && ok; c0 += kChunkSteps) {
         const int c1 = min(c0 + kChunkSteps, t.n_steps);
@@ -446,11 +412,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     x[i >> 1] = pack_half2(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
                   }
                 }
-#if SPLITD_PDS_V4
-                transpose_chunks_8x8(x, lane);
-#else
                 transpose_chunks32_4x4(x, lane);
-#endif
               } else {
                 // t' of this thread's own row, packed to fp16, goes through the SAME 4 x 4 chunk transpose as the
                 // stores; P' was loaded in that layout already, so dS' is one packed multiply per register and
@@ -470,11 +432,7 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     x[i >> 1] = pack_half2(i > cl ? 0.f : a, i + 1 > cl ? 0.f : bb);
                   }
                 }
-#if SPLITD_PDS_V4
-                transpose_chunks_8x8(x, lane);
-#else
                 transpose_chunks32_4x4(x, lane);
-#endif
 #pragma unroll
                 for (int w = 0; w < 32; ++w) x[w] = mul_half2(x[w], pq[h2 * 32 + w]);
                 if (j + 1 < c1) load_p_half(j + 1, h2);  // these registers are free again: next step's P
@@ -482,15 +440,9 @@ splitd_bwd_pds2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               // 64 keys x 2 bytes = 4 chunks of 32 bytes per row; after the transpose every 256-bit store
               // instruction of the warp writes whole 128-byte lines
               if (tile_valid) {
-#if SPLITD_PDS_V4
-                uint16_t* dst = ws_row + (mode ? plane : 0) + row_delta0 + key0 + (lane & 7) * 8;
-#pragma unroll
-                for (int r = 0; r < 8; ++r) st_global_v4_hint(dst + r * p.ws_pitch, &x[4 * r], mode ? pol_stream : pol_keep);
-#else
                 uint16_t* dst = ws_row + (mode ? plane : 0) + row_delta0 + key0 + (lane & 3) * 16;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) st_global_v8_hint(dst + r * p.ws_pitch, &x[8 * r], mode ? pol_stream : pol_keep);
-#endif
               }
             }
             if (prof) (mode ? t_m1 : t_m0) += clock64() - t1;

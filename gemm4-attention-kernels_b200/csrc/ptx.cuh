@@ -112,18 +112,6 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, P;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // A wait gives up after this long. It is far beyond anything a healthy kernel waits for (the longest legitimate
 // wait is one tile of another role, well under 10 ms) but leaves room for a context that is time-sliced or
 // preempted for a while; a kernel whose peer never arrives still ends instead of hanging the GPU.
@@ -170,28 +158,10 @@ __device__ __forceinline__ void tc_fence_before_sync() {
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 // ----------------------------------------------------------------------------------------------
 // TMA tiled loads (no multicast). The mbarrier may belong to the leader CTA of a CTA pair:
 // the .cta_group::2 form lets the completion signal a barrier in the peer CTA.
 // ----------------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                            int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                            int c2, int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0,
                                                  int c1, int c2, int c3) {
   asm volatile(
@@ -249,16 +219,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 // K-major operand ([rows][64 elems], 128 B per row): SBO = 1024 (8-row group pitch), LBO unused (1).
 // MN-major operand ([k][64 elems of M/N], 128 B per k): SBO = 1024 (8-k group pitch),
 //   LBO = byte distance between consecutive 64-element blocks along M/N.
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-
 // Split form for issue loops: the high word is the same for every 128B-swizzled operand with an
 // 8-row group pitch of 1024 bytes; the low word is (address >> 4) | (LBO >> 4) << 16 and can be advanced
 // by adding (byte offset >> 4). Keeping these in registers makes one MMA issue a handful of instructions,
@@ -275,13 +235,11 @@ __device__ __forceinline__ uint64_t desc_join(uint32_t lo) {
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major  [16] B major (0 = K-major, 1 = MN-major)  [17,23) N >> 3  [24,29) M >> 4
-// A and B have format fields of their own: the two operands of one MMA may differ (fp16 x bf16).
-__host__ __device__ constexpr uint32_t make_idesc_ab(bool a_fp16, bool b_fp16, bool a_mn, bool b_mn, int M, int N) {
-  return (1u << 4) | ((a_fp16 ? 0u : 1u) << 7) | ((b_fp16 ? 0u : 1u) << 10) | ((a_mn ? 1u : 0u) << 15) |
-         ((b_mn ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
-}
+// A and B get the same format: an MMA whose A is fp16 and whose B is bf16 raises an illegal-instruction fault on
+// B200 (it was tried), although the descriptor has a field for each.
 __host__ __device__ constexpr uint32_t make_idesc(bool fp16, bool a_mn, bool b_mn, int M, int N) {
-  return make_idesc_ab(fp16, fp16, a_mn, b_mn, M, N);
+  return (1u << 4) | ((fp16 ? 0u : 1u) << 7) | ((fp16 ? 0u : 1u) << 10) | ((a_mn ? 1u : 0u) << 15) |
+         ((b_mn ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
 template <int kCtaGroup>
@@ -301,29 +259,8 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         : "memory");
 }
 
-// A operand from tensor memory (rows = TMEM lanes, 16-bit elements packed two per column).
-template <int kCtaGroup>
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  if constexpr (kCtaGroup == 1)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Completion of all prior MMAs of this thread arrives (count 1) on the mbarrier.
-__device__ __forceinline__ void umma_commit_1sm(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// Pair form: arrives on the barrier at this offset in every CTA named by `cta_mask`.
+// Completion of all prior MMAs of this thread arrives (count 1) on the mbarrier at this offset in every CTA named
+// by `cta_mask` (an mbarrier arrive that is multicast, not a copy).
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -371,11 +308,6 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 // tanh to ~1e-6 absolute: (1 - e) / (1 + e) with e = exp(-2|x|). tanh.approx.f32 is only good to ~2^-11
 // relative, which a softcap of 15 turns into 0.7 % on the probabilities.
 __device__ __forceinline__ float tanh_precise(float x) {
@@ -410,32 +342,10 @@ __device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, ui
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// x holds 8 chunks of 16 bytes (4 words each) of ONE row per thread: x[4*c .. 4*c+3] = chunk c of row `lane`.
-// After the call, x[4*r .. 4*r+3] in lane l is chunk (l & 7) of row (lane & ~7) + r: an 8 x 8 transpose of
-// chunks inside every group of 8 lanes (3 butterfly rounds of warp shuffles). A store of word group r then
-// has 8 consecutive lanes writing one full 128-byte line, 4 lines per warp instruction instead of 32
+// x[8*c .. 8*c+7] = 32-byte chunk c (of 4) of ONE row per thread; afterwards x[8*r .. 8*r+7] in lane l is chunk
+// (l & 3) of row (lane & ~3) + r: a 4 x 4 transpose of chunks inside every group of 4 lanes (2 butterfly rounds of
+// warp shuffles). With 256-bit stores a warp then writes 8 full 128-byte lines per instruction instead of 32
 // partial ones.
-__device__ __forceinline__ void transpose_chunks_8x8(uint32_t (&x)[32], int lane) {
-#pragma unroll
-  for (int m = 1; m < 8; m <<= 1) {
-    const bool up = (lane & m) != 0;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      if (c & m) continue;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint32_t a = x[4 * c + w], b = x[4 * (c | m) + w];
-        const uint32_t recv = __shfl_xor_sync(0xffffffffu, up ? a : b, m);
-        x[4 * c + w] = up ? recv : a;
-        x[4 * (c | m) + w] = up ? b : recv;
-      }
-    }
-  }
-}
-
-// Same idea with 32-byte chunks: x[8*c .. 8*c+7] = chunk c (of 4) of ONE row per thread; afterwards
-// x[8*r .. 8*r+7] in lane l is chunk (l & 3) of row (lane & ~3) + r. With 256-bit stores a warp then writes
-// 8 full 128-byte lines per instruction.
 __device__ __forceinline__ void transpose_chunks32_4x4(uint32_t (&x)[32], int lane) {
 #pragma unroll
   for (int m = 1; m < 4; m <<= 1) {
