@@ -211,8 +211,9 @@ def run_ours(args):
             out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True)
             evs = []
             I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs)
-            # forward; row maxima + preprocess; per chunk of the backward: P/dS tiles, gradient GEMMs
-            launches += 1 + 2 + (len(evs) - 2)
+            # forward (fp16 copy of v + attention kernel); row maxima + preprocess; per chunk of the backward:
+            # P/dS tiles, gradient GEMMs
+            launches += 2 + 2 + (len(evs) - 2)
             if record is not None:
                 record.append(((B, S, causal), [("fwd", e0)] + evs))
         return launches
