@@ -45,6 +45,13 @@ SWEEP = [(16, 1024), (8, 2048), (4, 4096), (2, 8192), (1, 16384)]
 METRIC = "D512 GQA attn fwd+bwd TFLOP/s (bf16, B*S=16K sweep)"
 
 
+def fwd_train(I, q, k, v, causal, **kw):
+    """The forward as autograd runs it when a backward will follow: (out, lse, low-word scratch or None)."""
+    if I._KEEP_RESIDUAL:
+        return I._flash_attn_fwd(q, k, v, causal=causal, return_lse=True, keep_resid=True, **kw)
+    return I._flash_attn_fwd(q, k, v, causal=causal, return_lse=True, **kw) + (None,)
+
+
 def flops_fwd(B, S, causal):
     return 4.0 * B * HQ * S * S * D * (0.5 if causal else 1.0)
 
@@ -208,9 +215,9 @@ def run_ours(args):
             qq, kk, vv, dd = q.view(B, S, HQ, D), k.view(B, S, HKV, D), v.view(B, S, HKV, D), do.view(B, S, HQ, D)
             e0 = torch.cuda.Event(enable_timing=True)
             e0.record()
-            out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True)
+            out, lse, resid = fwd_train(I, qq, kk, vv, causal)
             evs = []
-            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs)
+            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs, out_resid=resid)
             # forward (fp16 copy of v + attention kernel); row maxima + preprocess; per chunk of the backward:
             # P/dS tiles, gradient GEMMs
             launches += 2 + 2 + (len(evs) - 2)
@@ -378,10 +385,13 @@ def run_ours(args):
     def fwd_bwd_events(qq, kk, vv, dd, causal, backward=True, **kw):
         e0 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True, **kw)
+        if backward:
+            out, lse, resid = fwd_train(I, qq, kk, vv, causal, **kw)
+        else:
+            out, lse = I._flash_attn_fwd(qq, kk, vv, causal=causal, return_lse=True, **kw)
         evs = [("fwd", e0)]
         if backward:
-            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs, **kw)
+            I._flash_attn_bwd(qq, kk, vv, out, dd, lse, causal=causal, stage_events=evs, out_resid=resid, **kw)
         else:
             e1 = torch.cuda.Event(enable_timing=True)
             e1.record()
@@ -426,12 +436,13 @@ def run_ours(args):
             outs = []
             for s_id in ids:
                 qs, ks, vs = sharding.shard_views(lq, lk, lv, shards[s_id], HQ, HKV)
-                outs.append((s_id,) + I._flash_attn_fwd(qs, ks, vs, causal=True, return_lse=True))
+                outs.append((s_id,) + fwd_train(I, qs, ks, vs, True))
             e[1].record()
-            for s_id, out, lse in outs:
+            for s_id, out, lse, resid in outs:
                 b, g = shards[s_id]
                 qs, ks, vs = sharding.shard_views(lq, lk, lv, shards[s_id], HQ, HKV)
-                grads = I._flash_attn_bwd(qs, ks, vs, out, ldo[b : b + 1, :, g * G : (g + 1) * G], lse, causal=True)
+                grads = I._flash_attn_bwd(qs, ks, vs, out, ldo[b : b + 1, :, g * G : (g + 1) * G], lse, causal=True,
+                                          out_resid=resid)
                 if keep is not None:
                     keep[s_id] = (out, lse) + tuple(grads)
             e[2].record()
@@ -584,14 +595,17 @@ def run_case(args):
     for it in range(args.iters):
         e0 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        out, lse = I._flash_attn_fwd(q, k, v, causal=causal, return_lse=True, **kw)
+        if args.no_backward:
+            out, lse = I._flash_attn_fwd(q, k, v, causal=causal, return_lse=True, **kw)
+        else:
+            out, lse, resid = fwd_train(I, q, k, v, causal, **kw)
         evs = [("fwd", e0)]
         if args.no_backward:
             e1 = torch.cuda.Event(enable_timing=True)
             e1.record()
             evs.append(("end", e1))
         else:
-            I._flash_attn_bwd(q, k, v, out, do, lse, causal=causal, stage_events=evs, **kw)
+            I._flash_attn_bwd(q, k, v, out, do, lse, causal=causal, stage_events=evs, out_resid=resid, **kw)
         torch.cuda.synchronize()
         ts = {}
         for (label, ev), (_, nxt) in zip(evs[:-1], evs[1:]):

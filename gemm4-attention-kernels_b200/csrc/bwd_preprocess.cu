@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) splitd_bwd_rowmax_kernel(const BwdParams 
   flush();
 }
 
-__global__ void __launch_bounds__(256) splitd_bwd_preprocess_kernel(const BwdParams p, int q_blocks, int q_chunks,
+__global__ void __launch_bounds__(256, 3) splitd_bwd_preprocess_kernel(const BwdParams p, int q_blocks, int q_chunks,
                                                                     int k_chunks) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const TileGeom& g = p.g;
@@ -139,21 +139,26 @@ __global__ void __launch_bounds__(256) splitd_bwd_preprocess_kernel(const BwdPar
     for (int hg = 0; hg < g.group; ++hg) {
       const int head = pb.kvh * g.group + hg;
       const int64_t bo = pb.packed ? 0 : b;
-      const Row16 o = load_row(reinterpret_cast<const uint16_t*>(p.o) + bo * p.o_stride_b +
-                                   static_cast<int64_t>(tok) * p.o_stride_s + head * p.o_stride_h, lane);
+      Row16 o = load_row(reinterpret_cast<const uint16_t*>(p.o) + bo * p.o_stride_b +
+                             static_cast<int64_t>(tok) * p.o_stride_s + head * p.o_stride_h, lane);
       const Row16 d = load_row(reinterpret_cast<const uint16_t*>(p.dout) + bo * p.do_stride_b +
                                    static_cast<int64_t>(tok) * p.do_stride_s + head * p.do_stride_h, lane);
       const Row16 qr = load_row(reinterpret_cast<const uint16_t*>(p.q) + bo * p.q_stride_b +
                                     static_cast<int64_t>(tok) * p.q_stride_s + head * p.q_stride_h, lane);
       const int64_t row = (bo * pb.n_tok + tok) * g.heads_q + head;  // contiguous (B,S,H,512) / (T,H,512) copies
+      const int64_t idx = pb.packed ? static_cast<int64_t>(head) * p.total_q + tok
+                                    : (static_cast<int64_t>(b) * g.heads_q + head) * g.seqlen_q + tok;
+      if (p.resid_rows != nullptr && p.resid_flags[idx] != 0) {  // the low word the forward kept of this row
+        const Row16 lo = load_row(p.resid_rows + row * kHeadDim, lane);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o.x[e] += lo.x[e];
+      }
       store_row_half(p.do_h + row * kHeadDim, lane, d, do_mul);
       store_row_half(p.q_h + row * kHeadDim, lane, qr, 1.f);
       float acc = 0.f;
 #pragma unroll
       for (int e = 0; e < 16; ++e) acc = fmaf(o.x[e], d.x[e], acc);
       acc = warp_sum(acc);
-      const int64_t idx = pb.packed ? static_cast<int64_t>(head) * p.total_q + tok
-                                    : (static_cast<int64_t>(b) * g.heads_q + head) * g.seqlen_q + tok;
       if (p.dlse) acc -= p.dlse[idx];
       if (lane == 0) {
         const float l = p.lse[idx];
@@ -321,6 +326,10 @@ int fill_bwd_params(const splitd_params* p, BwdParams& bp, const BwdPlan* pl) {
   bp.dpsum = p->dpsum;
   bp.lse_log2 = p->lse_log2;
   bp.o = p->o;
+  bp.resid_flags = static_cast<const uint8_t*>(p->o_resid);
+  bp.resid_rows = p->o_resid ? reinterpret_cast<const uint16_t*>(static_cast<const uint8_t*>(p->o_resid) +
+                                                                 out_resid_flag_bytes(p))
+                             : nullptr;
   bp.dout = p->dout;
   bp.q = p->q;
   bp.k = p->k;
@@ -345,6 +354,8 @@ int fill_bwd_params(const splitd_params* p, BwdParams& bp, const BwdPlan* pl) {
   for (auto q : ptrs)
     if (reinterpret_cast<uintptr_t>(q) % 16 != 0)
       return fail(SPLITD_ERR_INVALID_ARGUMENT, "q/k/v/o/dout/dq/dk/dv must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(p->o_resid) % 256 != 0)
+    return fail(SPLITD_ERR_INVALID_ARGUMENT, "o_resid must be 256-byte aligned");
   bp.total_q = p->total_q;
   bp.total_k = p->total_k;
   const bool varlen = p->cu_seqlens_q != nullptr;

@@ -181,6 +181,8 @@ int splitd_fwd(const splitd_params* p, void* stream) {
 size_t splitd_fwd_workspace_bytes(const splitd_params* p) { return p ? fwd_workspace_bytes(p) : 0; }
 
 size_t splitd_bwd_rowstat_elems(const splitd_params* p) { return p ? bwd_rowstat_elems(p) : 0; }
+
+size_t splitd_out_resid_bytes(const splitd_params* p) { return p ? out_resid_bytes(p) : 0; }
 size_t splitd_bwd_workspace_bytes(const splitd_params* p) { return p ? bwd_workspace_bytes(p) : 0; }
 size_t splitd_bwd_workspace_bytes_limit(const splitd_params* p, size_t tile_bytes_limit) {
   return p ? bwd_workspace_bytes_for(p, tile_bytes_limit) : 0;

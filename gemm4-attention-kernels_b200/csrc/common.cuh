@@ -40,6 +40,9 @@ struct TileGeom {
 struct FwdParams {
   TileGeom g;
   void* o;
+  uint8_t* resid_flags;  // optional low word of the output (exact output minus o, in the output dtype): one byte per
+  uint16_t* resid_rows;  // row (indexed like lse) saying whether the row's low word was written, and the rows,
+                         // contiguous (batch, position, head, 512) / (token, head, 512)
   float* lse;
   int64_t o_stride_b, o_stride_s, o_stride_h;  // elements
   int total_q;                                 // packed: T (lse row pitch)
@@ -72,6 +75,8 @@ struct BwdParams {
   float* dpsum;           // rowsum(dO*O) - dlse, same indexing as lse
   float* lse_log2;        // lse * log2(e), same indexing as lse
   const void* o;
+  const uint8_t* resid_flags;   // optional low word of o as the forward left it (see FwdParams): for a row whose
+  const uint16_t* resid_rows;   // flag is set, dpsum = rowsum(dO * (o + low word))
   const void* dout;
   const void* q;
   const void* k;

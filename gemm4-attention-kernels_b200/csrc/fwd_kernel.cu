@@ -67,6 +67,10 @@ static_assert(kSmemBytes <= 232448, "shared memory budget");
 constexpr int kTmemColsO = 0;
 constexpr int kTmemColsS = 256;
 constexpr float kRescaleThreshold = 8.0f;          // log2 units
+// A row whose largest probability exceeds this keeps the low word of its output for the backward (rows whose
+// probability mass sits on few keys have |out| ~ |v|, where the 16-bit rounding of out matters; below the
+// threshold the mass is spread over at least 16 keys)
+constexpr float kResidPmax = 1.f / 16.f;
 }  // namespace fwd
 
 // Slot tables kept in registers: nibble s of `tab` is the physical slot of logical ring stage s.
@@ -464,7 +468,8 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     // Epilogue of a tile: O / rowsum -> global memory, LSE. `has_acc` is false for a tile without visible keys
     // (zeros, LSE = -inf, no TMEM access). The caller has waited for the tile's last PV.
-    auto epilogue = [&](int e_b, int e_hu, int e_p0, int e_sq, int e_qoff, float m_ref, float l_sum, bool has_acc) {
+    auto epilogue = [&](int e_b, int e_hu, int e_p0, int e_sq, int e_qoff, float m_ref, float m_top, float l_sum,
+                        bool has_acc) {
       const int pos = e_p0 + static_cast<int>(rank) * g.pos_per_cta + (row >> pack_shift);
       const int head = e_hu * g.pack_g + (row & (g.pack_g - 1));
       float l_tot = 0.f;
@@ -477,10 +482,26 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         xphase ^= 1u;
         if (!ok) return;
-        l_tot = (l_sum + xs[xi ^ 64]) + (xs[xi ^ 128] + xs[xi ^ 192]);
+        // one order of summation for the row's four threads: they must agree on the decision below
+        l_tot = (xs[row] + xs[row + 64]) + (xs[row + 128] + xs[row + 192]);
       }
       const bool any = l_tot > 0.f;
       const float inv = any ? 1.f / l_tot : 0.f;
+      // Low word of the output: written for a group of 4 rows (the 4 lanes that store together; the same rows in the
+      // four warps that share them) when one of them is concentrated on few keys; a byte per row tells the backward
+      // whether it is there.
+      bool w_resid = false, g_resid = false;  // any group of the warp / this lane's group
+      if (p.resid_rows != nullptr) {
+        const bool peaked = any && ex2((m_top - m_ref) * p.scale_log2) * inv > kResidPmax;
+        const uint32_t votes = __ballot_sync(0xffffffffu, peaked);
+        w_resid = votes != 0u;
+        g_resid = ((votes >> (lane & ~3)) & 0xfu) != 0u;
+        if (pos < e_sq && half == 0 && wg == 0) {
+          const int64_t idx = g.cu_q ? static_cast<int64_t>(head) * p.total_q + e_qoff + pos
+                                     : (static_cast<int64_t>(e_b) * g.heads_q + head) * e_sq + pos;
+          p.resid_flags[idx] = g_resid ? 1 : 0;
+        }
+      }
       if (pos < e_sq && half == 0 && wg == 0 && p.lse != nullptr) {
         const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         const float lse = any ? (ms + lg2(l_tot)) * kLn2 : -INFINITY;
@@ -524,16 +545,41 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 64; i += 2)
           x[i >> 1] = pack2<kFp16>(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+        if (w_resid) {
+          // low word: what the rounding of the output dropped, rounded to 16 bits itself (t is overwritten in place)
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            float h0, h1;
+            unpack2<kFp16>(x[i >> 1], h0, h1);
+            t[i >> 1] = pack2<kFp16>(fmaf(__uint_as_float(t[i]), inv, -h0), fmaf(__uint_as_float(t[i + 1]), inv, -h1));
+          }
+        }
         transpose_chunks32_4x4(x, lane);
         // now x[8e..8e+7] = 32-byte chunk (lane & 3) of row grp_row0 + e
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           if (rowp[e] != nullptr) st_global_32b(rowp[e] + c2 * 64, &x[8 * e]);
+        if (w_resid) {
+          uint32_t(&y)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[0]);
+          transpose_chunks32_4x4(y, lane);
+          // rows of the low word are contiguous, (batch, position, head, 512) / (token, head, 512)
+          const int64_t tok0 = (g.cu_q ? 0 : static_cast<int64_t>(e_b) * e_sq) + e_qoff;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int re = grp_row0 + e;
+            const int pos_e = e_p0 + static_cast<int>(rank) * g.pos_per_cta + (re >> pack_shift);
+            const int head_e = e_hu * g.pack_g + (re & (g.pack_g - 1));
+            if (g_resid && pos_e < e_sq)
+              st_global_32b(p.resid_rows + ((tok0 + pos_e) * g.heads_q + head_e) * kHeadDim + wg * 256 + half * 128 +
+                                (lane & 3) * 16 + c2 * 64,
+                            &y[8 * e]);
+          }
+        }
       }
     };
 
     int prev_b = 0, prev_hu = 0, prev_p0 = 0, prev_sq = 0, prev_qoff = 0;  // what the owed epilogue needs of its tile
-    float prev_m = 0.f, prev_l = 0.f;
+    float prev_m = 0.f, prev_mt = 0.f, prev_l = 0.f;
     bool have_prev = false;  // a tile whose steps are done but whose epilogue has not run yet
     long long t_epi = 0;
 
@@ -549,9 +595,9 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (!ok) break;
           tc_fence_after_sync();
           have_prev = false;
-          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_l, true);
+          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_mt, prev_l, true);
         }
-        if (more && ok) epilogue(tc.b, tc.hu, tc.p0, tc.sq, tc.q_off, -INFINITY, 0.f, false);
+        if (more && ok) epilogue(tc.b, tc.hu, tc.p0, tc.sq, tc.q_off, -INFINITY, -INFINITY, 0.f, false);
         if (!more) break;
         continue;
       }
@@ -559,7 +605,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       int limit = tc.sk - 1;  // last visible key of this row
       if (p.win_right >= 0) limit = min(limit, pos + tc.sk - tc.sq + p.win_right);
       const int lo_limit = p.win_left >= 0 ? pos + tc.sk - tc.sq - p.win_left : 0;  // first visible key
-      float m_ref = -INFINITY, l_sum = 0.f;
+      float m_ref = -INFINITY, m_top = -INFINITY, l_sum = 0.f;  // m_top: the row's largest score so far
 
       for (int j = 0; j < n_steps && ok; ++j, ++gs) {
         long long t0 = prof ? clock64() : 0;
@@ -610,6 +656,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!ok) break;
         mx = fmaxf(fmaxf(mx, xs[xi ^ 64]), fmaxf(xs[xi ^ 128], xs[xi ^ 192]));
 
+        m_top = fmaxf(m_top, mx);
         float factor = 1.f;
         bool rescale = false;
         if (m_ref == -INFINITY) {
@@ -677,7 +724,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           // the tensor pipe works on the previous tile's last PV while the first softmax step runs, and on
           // this tile's first PV (as soon as O has been read) while the stores of the epilogue drain.
           const long long te = prof ? clock64() : 0;
-          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_l, true);
+          epilogue(prev_b, prev_hu, prev_p0, prev_sq, prev_qoff, prev_m, prev_mt, prev_l, true);
           if (prof) t_epi += clock64() - te;
           have_prev = false;
           if (!ok) break;
@@ -690,6 +737,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prev_sq = tc.sq;
       prev_qoff = tc.q_off;
       prev_m = m_ref;
+      prev_mt = m_top;
       prev_l = l_sum;
       have_prev = true;
     }
@@ -780,7 +828,12 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   if (reinterpret_cast<uintptr_t>(p->o) % 16 != 0 || p->o_strides[1] % 8 != 0 || p->o_strides[2] % 8 != 0 ||
       p->o_strides[0] % 8 != 0)
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "o must be 16-byte aligned with strides that are multiples of 8 elements");
+  if (reinterpret_cast<uintptr_t>(p->o_resid) % 256 != 0)
+    return fail(SPLITD_ERR_INVALID_ARGUMENT, "o_resid must be 256-byte aligned");
   fp.o = p->o;
+  fp.resid_flags = static_cast<uint8_t*>(p->o_resid);
+  fp.resid_rows = p->o_resid ? reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(p->o_resid) + out_resid_flag_bytes(p))
+                             : nullptr;
   fp.lse = p->lse;
   fp.o_stride_b = p->o_strides[0];
   fp.o_stride_s = p->o_strides[1];

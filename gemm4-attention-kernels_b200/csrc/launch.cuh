@@ -49,6 +49,12 @@ int launch_bwd_chunk(const splitd_params* p, const BwdPlan& pl, int chunk, int s
 int launch_bwd_pds(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream);
 int launch_bwd_grad(const splitd_params* p, const BwdPlan& pl, int chunk, cudaStream_t stream, int modes);
 size_t bwd_rowstat_elems(const splitd_params* p);
+// The optional low word of the output (splitd_params::o_resid): a flag byte per output row (indexed like lse),
+// padded to 256 bytes, then one 512-element row per output row.
+inline size_t out_resid_flag_bytes(const splitd_params* p) { return (bwd_rowstat_elems(p) + 255) / 256 * 256; }
+inline size_t out_resid_bytes(const splitd_params* p) {
+  return out_resid_flag_bytes(p) + bwd_rowstat_elems(p) * static_cast<size_t>(kHeadDim) * 2;
+}
 size_t bwd_workspace_bytes(const splitd_params* p);
 size_t bwd_workspace_bytes_full(const splitd_params* p);
 size_t bwd_workspace_bytes_for(const splitd_params* p, size_t plane_limit);

@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = (
     "splitd_fwd",
     "splitd_fwd_workspace_bytes",
     "splitd_bwd_rowstat_elems",
+    "splitd_out_resid_bytes",
     "splitd_bwd_workspace_bytes",
     "splitd_bwd_workspace_bytes_limit",
     "splitd_bwd_num_chunks",
@@ -87,6 +88,7 @@ class SplitdParams(ctypes.Structure):
         ("local", ctypes.c_int32),
         ("window_left", ctypes.c_int32),
         ("window_right", ctypes.c_int32),
+        ("o_resid", ctypes.c_void_p),
     ]
 
 
@@ -126,7 +128,12 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [pp, ctypes.c_void_p]
         fn.restype = ctypes.c_int
-    for name in ("splitd_fwd_workspace_bytes", "splitd_bwd_rowstat_elems", "splitd_bwd_workspace_bytes"):
+    for name in (
+        "splitd_fwd_workspace_bytes",
+        "splitd_bwd_rowstat_elems",
+        "splitd_out_resid_bytes",
+        "splitd_bwd_workspace_bytes",
+    ):
         fn = getattr(lib, name)
         fn.argtypes = [pp]
         fn.restype = ctypes.c_size_t

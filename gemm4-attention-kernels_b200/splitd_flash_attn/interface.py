@@ -30,6 +30,7 @@ __all__ = [
     "kernel_status",
     "cu_seqlens_validation",
     "set_backward_workspace_limit",
+    "set_output_residual",
 ]
 
 # Value checks of cu_seqlens (first entry 0, last entry = token count, non-decreasing, max_seqlen large enough)
@@ -60,6 +61,24 @@ def cu_seqlens_validation(enabled: bool):
 # Larger problems are processed in chunks that reuse the same memory; results do not depend on it.
 _env_limit = os.environ.get("SPLITD_BWD_WORKSPACE_LIMIT_BYTES")
 _WORKSPACE_LIMIT: Optional[int] = int(_env_limit) if _env_limit else None
+
+
+# A training forward keeps, for the output rows whose probability mass sits on few keys, the 16-bit remainder
+# (exact output - out). The backward's rowsum(dout * out) then sees those rows to ~16 significant bits instead
+# of 8. With the 16-bit output alone the rounding of `out` is the largest error in dq / dk for such rows (the
+# first rows of a causal sequence): 2.2x the error of a math-backend SDPA was measured there, against <= 1.3x
+# with the remainder. Costs a scratch tensor of the size of `out` kept until the backward has run (only the
+# flagged rows of it are ever written or read). SPLITD_OUTPUT_RESIDUAL=0 (or the setter) turns it off: the
+# backward is then the reference's, which reads the 16-bit output (src/interface.py:732-741).
+_KEEP_RESIDUAL = os.environ.get("SPLITD_OUTPUT_RESIDUAL", "1") != "0"
+
+
+def set_output_residual(enabled: bool) -> bool:
+    """Keep the low word of the output between forward and backward (default on). Returns the old setting."""
+    global _KEEP_RESIDUAL
+    old = _KEEP_RESIDUAL
+    _KEEP_RESIDUAL = bool(enabled)
+    return old
 
 
 def set_backward_workspace_limit(nbytes: Optional[int]) -> Optional[int]:
@@ -381,11 +400,15 @@ def _flash_attn_fwd(
     out=None,
     lse=None,
     debug=None,
+    keep_resid=False,
 ):
     """Forward host wrapper; same contract as ``_flash_attn_fwd_sm90`` (interface.py:362-554).
 
     ``pack_gqa`` is accepted for compatibility: heads are always folded into rows when the group
-    size allows it, which gives identical results.
+    size allows it, which gives identical results. With ``keep_resid=True`` a third value is returned: an
+    opaque uint8 tensor holding, for the output rows that are concentrated on few keys, the part of the exact
+    output that rounding ``out`` to 16 bits dropped; ``_flash_attn_bwd(out_resid=...)`` uses it for a
+    ``rowsum(dout * out)`` that is free of that rounding.
     """
     (batch_size, seqlen_q, total_q, seqlen_k, num_head, num_head_kv, host_cu_q, host_cu_k) = _validate_qkv_common(
         q, k, v, cu_seqlens_q, cu_seqlens_k
@@ -422,7 +445,8 @@ def _flash_attn_fwd(
         out.zero_()
         if lse is not None:
             lse.fill_(float("-inf"))
-        return out, lse
+        # no row has a low word: all flags zero
+        return (out, lse, torch.zeros(_resid_bytes(out), dtype=torch.uint8, device=device)) if keep_resid else (out, lse)
 
     params = _fill_params(
         q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, debug
@@ -434,13 +458,17 @@ def _flash_attn_fwd(
         params.window_left = -1 if window_size_left is None or window_size_left < 0 else int(window_size_left)
         params.window_right = -1 if window_size_right is None or window_size_right < 0 else int(window_size_right)
     lib = _capi.load_library()
+    out_resid = None
+    if keep_resid:
+        out_resid = torch.empty(lib.splitd_out_resid_bytes(ctypes.byref(params)), dtype=torch.uint8, device=device)
+        params.o_resid = _ptr(out_resid)
     n_ws = lib.splitd_fwd_workspace_bytes(ctypes.byref(params))  # fp16 copy of v (bf16 inputs only)
     if n_ws:
         workspace = torch.empty(n_ws, dtype=torch.uint8, device=device)
         params.workspace, params.workspace_bytes = _ptr(workspace), n_ws
     with torch.cuda.device(device):
         _capi.check(lib.splitd_fwd(ctypes.byref(params), _stream_ptr(device)))
-    return out, lse
+    return (out, lse, out_resid) if keep_resid else (out, lse)
 
 
 def _flash_attn_bwd(
@@ -462,10 +490,12 @@ def _flash_attn_bwd(
     dlse=None,
     stage_events=None,
     debug=None,
+    out_resid=None,
 ):
     """Backward host wrapper; same contract as ``_flash_attn_bwd_sm90`` (interface.py:652-888):
     preprocess, dQ and dK/dV launches on the current stream, dq/dk/dv in the input dtype with
-    dk/dv already reduced over the query heads of each KV head."""
+    dk/dv already reduced over the query heads of each KV head. ``out_resid``: the low word of ``out``
+    that the forward kept (optional, see ``_flash_attn_fwd``)."""
     _validate_device_arch(q.device)
     if softcap != 0.0:
         raise NotImplementedError("SplitD backward does not support softcap yet")
@@ -512,6 +542,12 @@ def _flash_attn_bwd(
     params.dk_strides[:] = _strides3(dk, packed)
     params.dv_strides[:] = _strides3(dv, packed)
     lib = _capi.load_library()
+    if out_resid is not None and out_resid.numel():
+        if out_resid.dtype != torch.uint8 or out_resid.device != device or not out_resid.is_contiguous():
+            raise TypeError("out_resid must be the uint8 tensor a forward with keep_resid=True returned")
+        if out_resid.numel() != lib.splitd_out_resid_bytes(ctypes.byref(params)):
+            raise ValueError("out_resid does not belong to a forward of this shape")
+        params.o_resid = _ptr(out_resid)
     n_stat = lib.splitd_bwd_rowstat_elems(ctypes.byref(params))
     if _WORKSPACE_LIMIT is None:
         n_ws = lib.splitd_bwd_workspace_bytes(ctypes.byref(params))
@@ -555,7 +591,8 @@ def _flash_attn_bwd(
 class FlashAttnFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, softmax_scale, causal, window_size, softcap, pack_gqa, return_lse):
-        out, lse = _flash_attn_fwd(
+        keep = _KEEP_RESIDUAL and any(ctx.needs_input_grad[:3])
+        out, lse, *rest = _flash_attn_fwd(
             q,
             k,
             v,
@@ -566,8 +603,10 @@ class FlashAttnFunc(torch.autograd.Function):
             softcap=softcap,
             pack_gqa=pack_gqa,
             return_lse=return_lse,
+            keep_resid=keep,
         )
-        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.has_resid = keep
+        ctx.save_for_backward(q, k, v, out, lse, *rest)
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.window_size = window_size
@@ -578,7 +617,8 @@ class FlashAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout, dlse):
-        q, k, v, out, lse = ctx.saved_tensors
+        q, k, v, out, lse = ctx.saved_tensors[:5]
+        resid = ctx.saved_tensors[5] if ctx.has_resid else None
         if not ctx.return_lse:
             dlse = None
         if dout is None:
@@ -596,6 +636,7 @@ class FlashAttnFunc(torch.autograd.Function):
             window_size_left=ctx.window_size[0],
             window_size_right=ctx.window_size[1],
             dlse=dlse,
+            out_resid=resid,
         )
         return dq, dk, dv, None, None, None, None, None, None
 
@@ -691,6 +732,7 @@ def _varlen_bwd_custom(
     window_size_right: int,
     softcap: float,
     dlse: Optional[torch.Tensor],
+    out_resid: Optional[torch.Tensor] = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     return _flash_attn_bwd(
         q,
@@ -709,13 +751,14 @@ def _varlen_bwd_custom(
         max_seqlen_q=max_seqlen_q,
         max_seqlen_k=max_seqlen_k,
         dlse=dlse,
+        out_resid=out_resid,
     )
 
 
 @torch.library.register_fake("splitd_flash_attn::varlen_bwd")
 def _varlen_bwd_fake(
     q, k, v, out, dout, lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
-    window_size_left, window_size_right, softcap, dlse,
+    window_size_left, window_size_right, softcap, dlse, out_resid=None,
 ):
     _fake_shapes(q, k, v, cu_seqlens_q, cu_seqlens_k)
     if q.dtype == torch.float16:
@@ -813,6 +856,7 @@ def _bwd_custom(
     window_size_right: int,
     softcap: float,
     dlse: Optional[torch.Tensor],
+    out_resid: Optional[torch.Tensor] = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     return _flash_attn_bwd(
         q,
@@ -827,11 +871,14 @@ def _bwd_custom(
         window_size_left=_dec(window_size_left),
         window_size_right=_dec(window_size_right),
         dlse=dlse,
+        out_resid=out_resid,
     )
 
 
 @torch.library.register_fake("splitd_flash_attn::bwd")
-def _bwd_fake(q, k, v, out, dout, lse, softmax_scale, causal, window_size_left, window_size_right, softcap, dlse):
+def _bwd_fake(
+    q, k, v, out, dout, lse, softmax_scale, causal, window_size_left, window_size_right, softcap, dlse, out_resid=None
+):
     _fake_shapes_batched(q, k, v)
     if q.dtype == torch.float16:
         raise NotImplementedError("SplitD backward currently supports bfloat16 only.")
@@ -863,8 +910,159 @@ torch.library.register_autograd("splitd_flash_attn::fwd", _batched_backward, set
 
 
 # ---------------------------------------------------------------------------
+# Training forwards that also return the low word of the output (see _KEEP_RESIDUAL): ``fwd_resid`` and
+# ``varlen_fwd_resid`` are ``fwd`` / ``varlen_fwd`` with a third result, and their backward hands it to the
+# ``bwd`` / ``varlen_bwd`` ops above. The two-result ops keep the reference's schemas (and its backward, which
+# reads the 16-bit output).
+# ---------------------------------------------------------------------------
+
+
+def _resid_bytes(out: torch.Tensor) -> int:
+    """Size of the low-word scratch of an output (what splitd_out_resid_bytes returns): a flag byte per row of
+    512, padded to 256 bytes, then a 16-bit row of 512 per row."""
+    rows = out.numel() // out.shape[-1]
+    return (rows + 255) // 256 * 256 + rows * out.shape[-1] * 2
+
+
+@torch.library.custom_op("splitd_flash_attn::fwd_resid", mutates_args=())
+def _fwd_resid_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    pack_gqa: bool,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _flash_attn_fwd(
+        q,
+        k,
+        v,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        softcap=softcap,
+        pack_gqa=pack_gqa,
+        return_lse=True,
+        keep_resid=True,
+    )
+
+
+@torch.library.register_fake("splitd_flash_attn::fwd_resid")
+def _fwd_resid_fake(q, k, v, softmax_scale, causal, window_size_left, window_size_right, softcap, pack_gqa):
+    out, lse = _fwd_fake(q, k, v, softmax_scale, causal, window_size_left, window_size_right, softcap, pack_gqa)
+    return out, lse, out.new_empty((_resid_bytes(out),), dtype=torch.uint8)
+
+
+def _batched_resid_setup_context(ctx, inputs, output) -> None:
+    q, k, v = inputs[:3]
+    ctx.softmax_scale, ctx.causal, ctx.window_size_left, ctx.window_size_right, ctx.softcap = inputs[3:8]
+    out, lse, resid = output
+    ctx.save_for_backward(q, k, v, out, lse, resid)
+    ctx.set_materialize_grads(False)
+
+
+def _batched_resid_backward(ctx, dout, dlse, _dresid):
+    q, k, v, out, lse, resid = ctx.saved_tensors
+    if dout is None:
+        dout = torch.zeros_like(out)
+    dq, dk, dv = torch.ops.splitd_flash_attn.bwd(
+        q, k, v, out, dout, lse, ctx.softmax_scale, ctx.causal, ctx.window_size_left, ctx.window_size_right,
+        ctx.softcap, dlse, resid,
+    )
+    return dq, dk, dv, *((None,) * 6)
+
+
+torch.library.register_autograd(
+    "splitd_flash_attn::fwd_resid", _batched_resid_backward, setup_context=_batched_resid_setup_context
+)
+
+
+@torch.library.custom_op("splitd_flash_attn::varlen_fwd_resid", mutates_args=())
+def _varlen_fwd_resid_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: float,
+    causal: bool,
+    window_size_left: int,
+    window_size_right: int,
+    softcap: float,
+    pack_gqa: bool,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _flash_attn_fwd(
+        q,
+        k,
+        v,
+        cu_seqlens_q=cu_seqlens_q,
+        cu_seqlens_k=cu_seqlens_k,
+        max_seqlen_q=max_seqlen_q,
+        max_seqlen_k=max_seqlen_k,
+        softmax_scale=softmax_scale,
+        causal=causal,
+        window_size_left=_dec(window_size_left),
+        window_size_right=_dec(window_size_right),
+        softcap=softcap,
+        pack_gqa=pack_gqa,
+        return_lse=True,
+        keep_resid=True,
+    )
+
+
+@torch.library.register_fake("splitd_flash_attn::varlen_fwd_resid")
+def _varlen_fwd_resid_fake(
+    q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, window_size_left,
+    window_size_right, softcap, pack_gqa,
+):
+    out, lse = _varlen_fwd_fake(
+        q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, softmax_scale, causal, window_size_left,
+        window_size_right, softcap, pack_gqa,
+    )
+    return out, lse, out.new_empty((_resid_bytes(out),), dtype=torch.uint8)
+
+
+def _varlen_resid_setup_context(ctx, inputs, output) -> None:
+    q, k, v, cu_seqlens_q, cu_seqlens_k = inputs[:5]
+    ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal = inputs[5:9]
+    ctx.window_size_left, ctx.window_size_right, ctx.softcap = inputs[9:12]
+    out, lse, resid = output
+    ctx.save_for_backward(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k, resid)
+    ctx.set_materialize_grads(False)
+
+
+def _varlen_resid_backward(ctx, dout, dlse, _dresid):
+    q, k, v, out, lse, cu_q, cu_k, resid = ctx.saved_tensors
+    if dout is None:
+        dout = torch.zeros_like(out)
+    dq, dk, dv = torch.ops.splitd_flash_attn.varlen_bwd(
+        q, k, v, out, dout, lse, cu_q, cu_k, ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.softmax_scale, ctx.causal,
+        ctx.window_size_left, ctx.window_size_right, ctx.softcap, dlse, resid,
+    )
+    return dq, dk, dv, *((None,) * 10)
+
+
+torch.library.register_autograd(
+    "splitd_flash_attn::varlen_fwd_resid", _varlen_resid_backward, setup_context=_varlen_resid_setup_context
+)
+
+
+# ---------------------------------------------------------------------------
 # public API
 # ---------------------------------------------------------------------------
+
+
+def _wants_residual(q, k, v) -> bool:
+    """A forward whose result can be differentiated keeps the low word of the output (if that is switched on)."""
+    return _KEEP_RESIDUAL and torch.is_grad_enabled() and any(
+        isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v)
+    )
 
 
 def _reject_unsupported_training(q, k, v, softcap, window_size) -> None:
@@ -907,7 +1105,8 @@ def split_flash_attn_func(
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
     if pack_gqa is None:
         pack_gqa = q.ndim == 4 and k.ndim == 4 and q.shape[-2] > k.shape[-2]
-    out, lse = torch.ops.splitd_flash_attn.fwd(
+    op = torch.ops.splitd_flash_attn.fwd_resid if _wants_residual(q, k, v) else torch.ops.splitd_flash_attn.fwd
+    out, lse = op(
         q,
         k,
         v,
@@ -917,7 +1116,7 @@ def split_flash_attn_func(
         _enc(window_size[1]),
         float(softcap),
         bool(pack_gqa),
-    )
+    )[:2]
     return (out, lse) if return_lse else out
 
 
@@ -960,7 +1159,8 @@ def split_flash_attn_varlen_func(
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
     if pack_gqa is None:
         pack_gqa = q.shape[-2] > k.shape[-2]
-    out, lse = torch.ops.splitd_flash_attn.varlen_fwd(
+    op = torch.ops.splitd_flash_attn.varlen_fwd_resid if _wants_residual(q, k, v) else torch.ops.splitd_flash_attn.varlen_fwd
+    out, lse = op(
         q,
         k,
         v,
@@ -974,5 +1174,5 @@ def split_flash_attn_varlen_func(
         _enc(window_size[1]),
         float(softcap),
         bool(pack_gqa),
-    )
+    )[:2]
     return (out, lse) if return_lse else out

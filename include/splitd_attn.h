@@ -99,6 +99,18 @@ typedef struct {
   int32_t window_left;  /* >= 0: keys j < i + Sk - Sq - window_left are hidden; -1 = unbounded           */
   int32_t window_right; /* >= 0: keys j > i + Sk - Sq + window_right are hidden; -1 = unbounded          */
                         /* (sliding window of src/block_info.py:44-59; `causal` is window_right = 0)      */
+
+  /* ---- optional low word of the output, may be NULL ---- */
+  void* o_resid; /* 256-byte aligned scratch of splitd_out_resid_bytes() bytes that travels from the forward to the
+                    backward of the same call. Forward: for every output row whose probability mass is concentrated
+                    (largest probability > 1/16; decided per 4 rows) it receives (exact output - o), rounded to the
+                    16-bit dtype, plus a byte per row saying whether it did. Backward: for those rows
+                    dpsum = rowsum(dout * (o + low word)) instead of rowsum(dout * o). The rounding of o alone puts an
+                    error of about |dout| * sqrt(512) * ulp(o) / 3 into dpsum; for a row that sees few keys (the first
+                    rows of a causal sequence, |o| ~ |v|) that error, not the arithmetic of the kernels, decides the
+                    error of dq and dk. The reference (like every backward that reads the 16-bit o,
+                    src/interface.py:732-741) has it; a caller that carries o_resid from forward to backward does
+                    not. The layout inside is private to the library. */
 } splitd_params;
 
 /* 1 if `device` can run this library (compute capability 10.x), 0 if not, <0 on CUDA error.
@@ -118,6 +130,11 @@ size_t splitd_fwd_workspace_bytes(const splitd_params* p);
  * query head), batch * heads_q * seqlen_q or heads_q * total_q, no padding (src/interface.py:747-753 pads the
  * reference's to multiples of 64 per sequence; here tail rows are masked in the kernels instead). */
 size_t splitd_bwd_rowstat_elems(const splitd_params* p);
+
+/* Bytes of the optional `o_resid` scratch (one flag byte per output row, padded to 256, then one 16-bit row of 512
+ * per output row). It is written by splitd_fwd and read by splitd_bwd / splitd_bwd_preprocess of the same problem;
+ * there is no counterpart in the reference, whose backward reads the 16-bit output only (src/interface.py:732-741). */
+size_t splitd_out_resid_bytes(const splitd_params* p);
 
 /* The backward's scratch. The reference's kernels recompute S and dP in every head_dim pass and need no more
  * than the two row vectors above (src/interface.py:747-753); this library computes them once and hands the

@@ -103,6 +103,42 @@ def test_batched_custom_op_traces_under_fake_tensors():
     assert hasattr(torch.ops.splitd_flash_attn, "fwd") and hasattr(torch.ops.splitd_flash_attn, "bwd")
 
 
+def test_training_forward_ops_return_the_low_word_of_the_output():
+    """A forward that can be differentiated goes through ``fwd_resid`` / ``varlen_fwd_resid``: the two-result
+    ops plus a third result, an opaque uint8 scratch (a flag byte per output row, padded to 256, then a 16-bit
+    remainder row per output row), which the backward ops take as a trailing optional argument. All of it traces without a GPU; a no-grad call stays on the two-result ops."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from splitd_flash_attn import interface as I
+
+    ops = torch.ops.splitd_flash_attn
+    none = -(2**31)
+    with FakeTensorMode():
+        q = torch.empty(2, 96, 8, D, dtype=torch.bfloat16, device="cuda")
+        kv = torch.empty(2, 80, 2, D, dtype=torch.bfloat16, device="cuda")
+        out, lse, resid = ops.fwd_resid(q, kv, kv, 0.05, True, none, none, 0.0, True)
+        assert out.shape == q.shape and resid.dtype == torch.uint8
+        assert resid.shape == (2 * 96 * 8 + 2 * 96 * 8 * D * 2,)  # 1536 flag bytes are a multiple of 256 already
+        gq, gk, gv = ops.bwd(q, kv, kv, out, out, lse, 0.05, True, none, none, 0.0, None, resid)
+        assert gq.shape == q.shape and gk.shape == kv.shape and gv.shape == kv.shape
+        qp = torch.empty(96, 8, D, dtype=torch.bfloat16, device="cuda")
+        kp = torch.empty(96, 2, D, dtype=torch.bfloat16, device="cuda")
+        cu = torch.empty(4, dtype=torch.int32, device="cuda")
+        out, lse, resid = ops.varlen_fwd_resid(qp, kp, kp, cu, cu, 40, 40, 0.05, True, none, none, 0.0, True)
+        assert out.shape == qp.shape and lse.shape == (8, 96) and resid.shape == (96 * 8 + 96 * 8 * D * 2,)
+        gq, gk, gv = ops.varlen_bwd(qp, kp, kp, out, out, lse, cu, cu, 40, 40, 0.05, True, none, none, 0.0, None, resid)
+        assert gq.shape == qp.shape and gk.shape == kp.shape
+        assert not I._wants_residual(q, kv, kv)
+        assert I._wants_residual(q.requires_grad_(True), kv, kv)
+        with torch.no_grad():
+            assert not I._wants_residual(q, kv, kv)
+        old = I.set_output_residual(False)
+        try:
+            assert not I._wants_residual(q, kv, kv)
+        finally:
+            I.set_output_residual(old)
+
+
 def test_backward_workspace_is_bounded_for_the_full_layer():
     """Sizing needs no GPU. The B=2, S=32768, Hq=32, Hkv=4 layer would need 275 GB for all of its P / dS tiles;
     the default workspace caps the tiles at 9 GiB and the smallest accepted one is the operand copies plus a
