@@ -43,6 +43,7 @@ struct FwdParams {
   uint8_t* resid_flags;  // optional low word of the output (exact output minus o, in the output dtype): one byte per
   uint16_t* resid_rows;  // row (indexed like lse) saying whether the row's low word was written, and the rows,
                          // contiguous (batch, position, head, 512) / (token, head, 512)
+  int resid_all;         // 1: every row keeps its low word, not only the concentrated ones
   float* lse;
   int64_t o_stride_b, o_stride_s, o_stride_h;  // elements
   int total_q;                                 // packed: T (lse row pitch)

@@ -492,7 +492,7 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // whether it is there.
       bool w_resid = false, g_resid = false;  // any group of the warp / this lane's group
       if (p.resid_rows != nullptr) {
-        const bool peaked = any && ex2((m_top - m_ref) * p.scale_log2) * inv > kResidPmax;
+        const bool peaked = any && (p.resid_all != 0 || ex2((m_top - m_ref) * p.scale_log2) * inv > kResidPmax);
         const uint32_t votes = __ballot_sync(0xffffffffu, peaked);
         w_resid = votes != 0u;
         g_resid = ((votes >> (lane & ~3)) & 0xfu) != 0u;
@@ -831,6 +831,7 @@ int launch_fwd(const splitd_params* p, cudaStream_t stream) {
   if (reinterpret_cast<uintptr_t>(p->o_resid) % 256 != 0)
     return fail(SPLITD_ERR_INVALID_ARGUMENT, "o_resid must be 256-byte aligned");
   fp.o = p->o;
+  fp.resid_all = p->o_resid_all;
   fp.resid_flags = static_cast<uint8_t*>(p->o_resid);
   fp.resid_rows = p->o_resid ? reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(p->o_resid) + out_resid_flag_bytes(p))
                              : nullptr;

@@ -89,6 +89,7 @@ class SplitdParams(ctypes.Structure):
         ("window_left", ctypes.c_int32),
         ("window_right", ctypes.c_int32),
         ("o_resid", ctypes.c_void_p),
+        ("o_resid_all", ctypes.c_int32),
     ]
 
 

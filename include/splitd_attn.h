@@ -111,6 +111,11 @@ typedef struct {
                     error of dq and dk. The reference (like every backward that reads the 16-bit o,
                     src/interface.py:732-741) has it; a caller that carries o_resid from forward to backward does
                     not. The layout inside is private to the library. */
+  int32_t o_resid_all; /* forward only. 0: the low word is kept for concentrated rows (above). 1: for every row. The
+                          rounding of o also matters when v (or k) has a common component that is large against its
+                          spread, e.g. v = 8 + N(0,1): every row then has |o| ~ 8 although no row is concentrated,
+                          and dq was measured at 11.6x the SDPA-MATH error with the default, 1.2x with 1. Costs the
+                          forward one more output-sized write (about 6 % at the B*S = 16384 sizes). */
 } splitd_params;
 
 /* 1 if `device` can run this library (compute capability 10.x), 0 if not, <0 on CUDA error.

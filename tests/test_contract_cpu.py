@@ -137,6 +137,8 @@ def test_training_forward_ops_return_the_low_word_of_the_output():
             assert not I._wants_residual(q, kv, kv)
         finally:
             I.set_output_residual(old)
+        assert I.set_output_residual("all") is True and I._wants_residual(q, kv, kv)
+        assert I.set_output_residual(True) == "all"
 
 
 def test_backward_workspace_is_bounded_for_the_full_layer():
