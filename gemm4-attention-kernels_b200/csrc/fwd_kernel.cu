@@ -524,6 +524,38 @@ splitd_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                      static_cast<int64_t>(head_e) * p.o_stride_h
                                : nullptr;
       }
+      if (has_acc && !w_resid) {
+        // The common case: read and pack both halves of the row first, so that O is handed back to the tensor pipe
+        // (the next tile's first PV) before the transposes and the stores, not in the middle of them.
+        uint32_t xa[32], xb[32];
+        {
+          uint32_t t[64];
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + 32, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 64; i += 2)
+            xa[i >> 1] = pack2<kFp16>(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + 64, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+          tmem_ld32(lane_addr + kTmemColsO + wg * 128 + 96, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(leader_o_free);
+#pragma unroll
+          for (int i = 0; i < 64; i += 2)
+            xb[i >> 1] = pack2<kFp16>(__uint_as_float(t[i]) * inv, __uint_as_float(t[i + 1]) * inv);
+        }
+        transpose_chunks32_4x4(xa, lane);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (rowp[e] != nullptr) st_global_32b(rowp[e], &xa[8 * e]);
+        transpose_chunks32_4x4(xb, lane);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (rowp[e] != nullptr) st_global_32b(rowp[e] + 64, &xb[8 * e]);
+        return;
+      }
 #pragma unroll 1
       for (int c2 = 0; c2 < 2; ++c2) {
         uint32_t t[64];
