@@ -216,3 +216,36 @@ def test_two_streams_side_by_side():
     for a, b in zip(alone, together):
         for x, y in zip(a, b):
             assert torch.equal(x, y)
+
+
+def test_public_functions_run_under_torch_compile_fullgraph():
+    """Both layouts are custom ops with fake kernels and registered autograd, so `torch.compile(fullgraph=True)`
+    traces through them without a graph break; the compiled forward + backward give the gradients of the eager run
+    bit for bit (the ops are opaque to the compiler; only the arithmetic around them is fused)."""
+    from splitd_flash_attn import split_flash_attn_func, split_flash_attn_varlen_func
+    from splitd_flash_attn.interface import cu_seqlens_validation
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+
+    def batched(q, k, v):
+        return split_flash_attn_func(q * 1.0, k, v, causal=True).float().square().sum()
+
+    q, k, v = mk(2, 256, 8, 512), mk(2, 256, 2, 512), mk(2, 256, 2, 512)
+    eager = torch.autograd.grad(batched(q, k, v), (q, k, v))
+    compiled = torch.autograd.grad(torch.compile(batched, fullgraph=True)(q, k, v), (q, k, v))
+    assert all(torch.equal(a, b) for a, b in zip(eager, compiled))
+
+    cu = torch.tensor([0, 100, 256, 300], dtype=torch.int32, device="cuda")
+
+    def packed(q, k, v):
+        return split_flash_attn_varlen_func(q * 1.0, k, v, cu, cu, 156, 156, causal=True).float().square().sum()
+
+    q, k, v = mk(300, 8, 512), mk(300, 2, 512), mk(300, 2, 512)
+    with cu_seqlens_validation(False):  # value checks of cu_seqlens need the host; a traced graph has none
+        eager = torch.autograd.grad(packed(q, k, v), (q, k, v))
+        compiled = torch.autograd.grad(torch.compile(packed, fullgraph=True)(q, k, v), (q, k, v))
+    assert all(torch.equal(a, b) for a, b in zip(eager, compiled))
+    from splitd_flash_attn.interface import kernel_status
+
+    assert kernel_status() == 0
