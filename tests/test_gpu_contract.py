@@ -249,3 +249,35 @@ def test_public_functions_run_under_torch_compile_fullgraph():
     from splitd_flash_attn.interface import kernel_status
 
     assert kernel_status() == 0
+
+
+def test_forward_and_backward_can_be_captured_in_a_cuda_graph():
+    """Nothing in the batched path synchronises, allocates outside torch's allocator or reads device values on the
+    host, so a forward + backward can be captured once and replayed on new data in the same buffers."""
+    from splitd_flash_attn import split_flash_attn_func
+    from splitd_flash_attn.interface import kernel_status
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(2, 512, 8, 512), mk(2, 512, 2, 512), mk(2, 512, 2, 512), mk(2, 512, 8, 512)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up outside the capture (first calls look up function attributes)
+        out = split_flash_attn_func(q, k, v, causal=True)
+        torch.autograd.grad(out, (q, k, v), do)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_g = split_flash_attn_func(q, k, v, causal=True)
+        grads_g = torch.autograd.grad(out_g, (q, k, v), do)
+    with torch.no_grad():
+        q.add_(0.5)
+        do.mul_(2.0)
+    graph.replay()
+    torch.cuda.synchronize()
+    out_e = split_flash_attn_func(q, k, v, causal=True)
+    grads_e = torch.autograd.grad(out_e, (q, k, v), do)
+    assert torch.equal(out_g, out_e) and all(torch.equal(a, b) for a, b in zip(grads_g, grads_e))
+    assert kernel_status() == 0
