@@ -281,3 +281,25 @@ def test_forward_and_backward_can_be_captured_in_a_cuda_graph():
     grads_e = torch.autograd.grad(out_e, (q, k, v), do)
     assert torch.equal(out_g, out_e) and all(torch.equal(a, b) for a, b in zip(grads_g, grads_e))
     assert kernel_status() == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensors_on_a_device_that_is_not_the_current_one():
+    """The launches follow the tensors' device, not torch's current device (the reference's kernels are launched on
+    the current stream of the tensors' device as well): same bits on cuda:1 as on cuda:0, current device unchanged."""
+    from splitd_flash_attn import split_flash_attn_func
+    from splitd_flash_attn.interface import kernel_status
+
+    res = {}
+    for dev in ("cuda:0", "cuda:1"):
+        g = torch.Generator(device=dev).manual_seed(0)
+        mk = lambda *s: torch.randn(*s, device=dev, generator=g).to(torch.bfloat16)
+        q, k, v, do = mk(2, 300, 8, 512), mk(2, 300, 2, 512), mk(2, 300, 2, 512), mk(2, 300, 8, 512)
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        out, lse = split_flash_attn_func(q, k, v, causal=True, return_lse=True)
+        grads = torch.autograd.grad(out, (q, k, v), do)
+        torch.cuda.synchronize(dev)
+        res[dev] = [t.cpu() for t in (out.detach(), lse) + tuple(grads)]
+    assert torch.cuda.current_device() == 0
+    assert all(torch.equal(a, b) for a, b in zip(res["cuda:0"], res["cuda:1"]))
+    assert kernel_status() == 0
