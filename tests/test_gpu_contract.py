@@ -302,4 +302,4 @@ def test_tensors_on_a_device_that_is_not_the_current_one():
         res[dev] = [t.cpu() for t in (out.detach(), lse) + tuple(grads)]
     assert torch.cuda.current_device() == 0
     assert all(torch.equal(a, b) for a, b in zip(res["cuda:0"], res["cuda:1"]))
-    assert kernel_status() == 0
+    assert kernel_status(torch.device("cuda:0")) == 0 and kernel_status(torch.device("cuda:1")) == 0
