@@ -549,7 +549,8 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "fwd+bwd sweep: Hq=32 Hkv=4 D=512, (B,S) in (16,1024),(8,2048),(4,4096),(2,8192),(1,16384), causal and non-causal",
                        "l2": "operands of every shape (1.2 GB) exceed the 126 MB L2", "per_rank": "same sweep, own seed",
-                       "also": "config5 = the B=2 S=32768 layer as 8 shards over the ranks (strong scaling)"},
+                       "also": "config5 = the B=2 S=32768 layer as 8 shards over the ranks (strong scaling)",
+                       "output_low_word": {True: "concentrated rows (default)", "all": "every row", False: "off"}[I._KEEP_RESIDUAL]},
             "fwd_tflops": fwd_tflops, "bwd_tflops": bwd_tflops,
             "fwd_frac_of_peak": fwd_tflops / peak, "bwd_frac_of_peak": bwd_tflops / peak,
             "frac_of_nominal_2250": {"fwd": fwd_tflops / 2250.0, "bwd": bwd_tflops / 2250.0},
